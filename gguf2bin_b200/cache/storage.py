@@ -9,8 +9,19 @@ every group has storage of its own:
   (page, kv head) panel of keys is contiguous, so a kernel streams it with full-width
   loads.  Page numbers are shared by all groups: page ``p`` of a sequence covers the same
   token range everywhere.
+  With ``planes == 1`` a page holds ONE panel per kv head, which a mixer reads both as keys
+  and as values (latents from which keys and values are projected): ``[layers, pages, 1,
+  kv_heads, page_size, head_dim]``.
 * ``StateNeed``: a fixed-size state per sequence (for mixers that carry a state instead
   of keys).  Storage ``[layers, slots, *shape]``, cleared when a slot is opened.
+  ``by_position``: the state is a ring whose places are indexed by token position, deep
+  enough that the step at position p overwrites nothing that a step at position p reads;
+  a decode step that was launched ahead can then be taken back (see ``engine/decode.py``).
+
+A schedule position may need several of these at once (latents by position AND a few rows of
+fixed-size state): its need is then a ``dict`` name -> need and its view a ``dict`` name -> view.
+A position that borrows another position's storage (``cache_of``) still gets the storage
+of the needs it states itself.
 
 Beside the groups there is one fixed-size record per slot, ``seq_state``
 (``[slots, SEQ_STATE_WORDS]`` int32): the sampler's key and draw counter live there, so
@@ -43,27 +54,31 @@ class KVNeed:
     n_kv_heads: int
     head_dim: int
     window: int = 0          # 0: every position is kept
+    planes: int = 2          # 2: keys and values; 1: one panel per kv head that is both
 
     @property
     def group_key(self):
-        return ("kv", self.n_kv_heads, self.head_dim, "window" if self.window else "full")
+        key = ("kv", self.n_kv_heads, self.head_dim, "window" if self.window else "full")
+        return key if self.planes == 2 else key + (f"{self.planes} plane",)
 
 
 @dataclass(frozen=True)
 class StateNeed:
     shape: tuple
     dtype: torch.dtype = torch.float32
+    by_position: bool = False      # a ring indexed by token position: one step back loses nothing
 
     @property
     def group_key(self):
-        return ("state", tuple(self.shape), self.dtype)
+        return ("state", tuple(self.shape), self.dtype) + (("by position",) if self.by_position else ())
 
 
 @dataclass
 class KVView:
     """What an attention mixer gets for one layer: the layer's K/V pages."""
-    pages: torch.Tensor       # [n_pages, 2, n_kv_heads, page_size, head_dim]
+    pages: torch.Tensor       # [n_pages, planes, n_kv_heads, page_size, head_dim]
     page_size: int
+    planes: int = 2
 
 
 @dataclass
@@ -90,17 +105,24 @@ class Cache:
         self.spare_page, self.spare_slot = n_pages, n_slots          # beyond what the table hands out
         self.groups: dict[tuple, dict] = {}
         self._layer_group: dict[int, tuple] = {}
+        self._layer_names: dict[int, tuple] = {}      # positions whose need is a dict: its names
         for layer, need in enumerate(needs):
             if need is None:
                 continue
-            g = self.groups.setdefault(need.group_key, {"need": need, "layers": []})
-            g["layers"].append(layer)
-            self._layer_group[layer] = (need.group_key, len(g["layers"]) - 1)
+            named = need.items() if isinstance(need, dict) else [(None, need)]
+            if isinstance(need, dict):
+                self._layer_names[layer] = tuple(k for k, v in need.items() if v is not None)
+            for name, one in named:
+                if one is None:
+                    continue
+                g = self.groups.setdefault(one.group_key, {"need": one, "layers": []})
+                g["layers"].append((layer, name))
+                self._layer_group[(layer, name)] = (one.group_key, len(g["layers"]) - 1)
         for key, g in self.groups.items():
             need, nl = g["need"], len(g["layers"])
             if isinstance(need, KVNeed):
                 g["storage"] = torch.zeros(
-                    (nl, n_pages + 1, 2, need.n_kv_heads, self.page_size, need.head_dim),
+                    (nl, n_pages + 1, need.planes, need.n_kv_heads, self.page_size, need.head_dim),
                     dtype=dtype, device=self.device)
             else:
                 g["storage"] = torch.zeros((nl, n_slots + 1) + tuple(need.shape), dtype=need.dtype,
@@ -129,14 +151,38 @@ class Cache:
         """The layer's part of its group's storage (made once: the storage never moves)."""
         v = self._views.get(layer, self)
         if v is self:
-            if layer not in self._layer_group:
-                v = None
+            if layer in self._layer_names:
+                v = {name: self._one_view(layer, name) for name in self._layer_names[layer]}
+            elif (layer, None) in self._layer_group:
+                v = self._one_view(layer, None)
             else:
-                key, idx = self._layer_group[layer]
-                g = self.groups[key]
-                v = (KVView(g["storage"][idx], self.page_size) if isinstance(g["need"], KVNeed)
-                     else StateView(g["storage"][idx]))
+                v = None
             self._views[layer] = v
+        return v
+
+    def _one_view(self, layer: int, name):
+        key, idx = self._layer_group[(layer, name)]
+        g = self.groups[key]
+        if isinstance(g["need"], KVNeed):
+            return KVView(g["storage"][idx], self.page_size, g["need"].planes)
+        return StateView(g["storage"][idx])
+
+    def view_for(self, position: int, owner: int):
+        """What the execution at schedule ``position`` gets when the storage of its mixer is that
+        of position ``owner``: the owner's view; and where views are dictionaries, its own
+        entries first and the owner's for every name it has none of."""
+        if owner == position:
+            return self.view(position)
+        key = ("for", position, owner)
+        v = self._views.get(key, self)
+        if v is self:
+            own, lent = self.view(position), self.view(owner)
+            if isinstance(own, dict) or isinstance(lent, dict):
+                v = dict(lent) if isinstance(lent, dict) else {}
+                v.update(own if isinstance(own, dict) else {})
+            else:
+                v = lent
+            self._views[key] = v
         return v
 
     def bytes(self) -> int:
@@ -144,6 +190,6 @@ class Cache:
                    for g in self.groups.values())
 
     def describe(self) -> str:
-        parts = [f"{len(g['layers'])} layers x {k[0]}{k[1:]}" for k, g in self.groups.items()]
+        parts = [f"{len(g['layers'])} x {k[0]}{k[1:]}" for k, g in self.groups.items()]
         return (f"cache: {self.n_pages} pages of {self.page_size} tokens, {self.n_slots} slots, "
                 f"{self.bytes() / 2**20:.1f} MiB, {self.dtype}; groups: " + "; ".join(parts))

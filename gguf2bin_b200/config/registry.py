@@ -1,4 +1,5 @@
-"""One registry from an architecture's name (``architectures[0]`` of config.json)
+"""One registry from an architecture's name (``architectures[0]`` of config.json, or its
+string ``architecture``)
 to the reader that turns config.json into a ``ModelSpec``."""
 from __future__ import annotations
 
@@ -49,6 +50,8 @@ def load_plugins() -> None:
 def model_spec_from_dict(d: Mapping[str, Any]) -> ModelSpec:
     load_plugins()
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]              # some configurations name theirs with one string
     if not archs or not isinstance(archs, (list, tuple)):
         raise ConfigError("config.json: 'architectures' is missing or empty; registered: "
                           + ", ".join(registered_architectures()))

@@ -45,12 +45,13 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a block arrangement around a mixer and a feed-forward, the norm
-    used in the block (``ffn_norm``: another one before the feed-forward, when the two
-    places differ), and the tensor-name prefix of the layer in the checkpoint."""
+    """One layer: a block arrangement around a mixer and a feed-forward (None, where the
+    arrangement allows a layer without one), the norm used in the block (``ffn_norm``: another
+    one before the feed-forward, when the two places differ), and the tensor-name prefix of
+    the layer in the checkpoint."""
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norm: PartSpec
     prefix: str
     ffn_norm: Optional[PartSpec] = None

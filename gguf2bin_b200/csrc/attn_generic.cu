@@ -11,6 +11,11 @@
 // Keys are visited in chunks of 32 that start at absolute positions that are multiples
 // of 32, with a running maximum and sum, so the arithmetic for a (token, head) depends
 // only on its own position: not on how the tokens were cut into steps, nor on the batch.
+//
+// Two options for other kinds of attention.  `sink` (one float per query head, or null): the
+// softmax's denominator gets one more term exp(sink_h), which has no key and no value and is
+// not scaled.  `planes` = 1: a page holds one panel per kv head that serves as keys AND as
+// values (attention over cached latents); 2: a panel of keys and a panel of values.
 #include "common.cuh"
 
 G2B_DEFINE_LAST_ERROR
@@ -23,7 +28,8 @@ __global__ void __launch_bounds__(AG_WARPS * 32)
 attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__restrict__ cache,
                     const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
                     const int *__restrict__ page_table, int P, int n_tokens, int nh, int nkv,
-                    int hd, int page_size, int window, float scale) {
+                    int hd, int page_size, int window, float scale,
+                    const float *__restrict__ sink, int planes) {
   pdl_launch();
   pdl_wait();
   __shared__ float qs[AG_WARPS][AG_MAX_HD];
@@ -47,8 +53,8 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
   const size_t head_stride = (size_t)page_size * hd;              // one (page, K|V, kv head) panel
   for (int base = (lo / 32) * 32; base <= pos; base += 32) {
     const int page = page_table[(size_t)b * P + base / page_size];
-    const T *kpanel = cache + (((size_t)page * 2 + 0) * nkv + kvh) * head_stride;
-    const T *vpanel = cache + (((size_t)page * 2 + 1) * nkv + kvh) * head_stride;
+    const T *kpanel = cache + (((size_t)page * planes + 0) * nkv + kvh) * head_stride;
+    const T *vpanel = cache + (((size_t)page * planes + (planes - 1)) * nkv + kvh) * head_stride;
     const int in_page = base % page_size;                         // chunk lies inside one page
     const int key = base + lane;
     const bool valid = key >= lo && key <= pos;
@@ -79,6 +85,7 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
     m = m_new;
   }
   T *op = out + (size_t)t * nh * hd + (size_t)h * hd;
+  if (sink) l += expf(sink[h] - m);                                // m is finite: the token's own key
   const float inv_l = 1.f / l;
 #pragma unroll
   for (int i = 0; i < AG_MAX_HD / 32; ++i) {
@@ -90,8 +97,10 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
 extern "C" int g2b_attn_generic(const void *q, void *out, int dtype, const void *cache,
                                 const int *tok_pos, const int *tok_seq, const int *page_table,
                                 int P, int n_tokens, int nh, int nkv, int hd, int page_size,
-                                int window, float scale, cudaStream_t stream) {
+                                int window, float scale, const float *sink, int planes,
+                                cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (planes != 1 && planes != 2) G2B_REFUSE("attn_generic: %d panels per page and kv head (1 or 2)", planes);
   if (hd <= 0 || hd > AG_MAX_HD) G2B_REFUSE("attn_generic: head_dim %d outside 1..%d", hd, AG_MAX_HD);
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_generic: %d heads are not a multiple of %d kv heads", nh, nkv);
   if (page_size <= 0 || page_size % 32)
@@ -101,11 +110,11 @@ extern "C" int g2b_attn_generic(const void *q, void *out, int dtype, const void 
   if (dtype == G2B_F32)
     g2b_launch(attn_generic_kernel<float>, dim3(blocks), dim3(AG_WARPS * 32), 0, stream, 
         (const float *)q, (float *)out, (const float *)cache, tok_pos, tok_seq, page_table, P,
-        n_tokens, nh, nkv, hd, page_size, window, scale);
+        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes);
   else if (dtype == G2B_BF16)
     g2b_launch(attn_generic_kernel<bf16>, dim3(blocks), dim3(AG_WARPS * 32), 0, stream, 
         (const bf16 *)q, (bf16 *)out, (const bf16 *)cache, tok_pos, tok_seq, page_table, P,
-        n_tokens, nh, nkv, hd, page_size, window, scale);
+        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes);
   else
     G2B_REFUSE("attn_generic: unknown dtype %d", dtype);
   return g2b_check_launch("attn_generic");

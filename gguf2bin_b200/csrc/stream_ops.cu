@@ -1,0 +1,434 @@
+// Kernels of the parts that sit around the products of a gated pre-norm layer with a latent
+// cache.  Everything here is memory-bound and computes in 32-bit; activations are read and
+// written in the compute type (float or bfloat16), the residual stream is float.
+//
+//   embed_pair_norm   x_t = E[tok_t] * s + G[row(tok_{t-1}, tok_t)], then x / sqrt(mean(x^2) + eps) * w
+//                     row(a, b) = (a * mul_prev + b * mul_cur) mod buckets; a sequence's first token
+//                     takes row `buckets`.  The previous token of a step's first token comes from a
+//                     two-place ring per slot that is indexed by position parity.
+//   canon_conv        u_t = h_t + sum_j w[:, j] * h_{t - taps + 1 + j} per channel, causal.  Rows before
+//                     the step's first come from a ring of `taps` rows per slot, indexed by
+//                     position mod taps; rows before the sequence's start are zero.
+//   latent_keep       c = rmsnorm(d) * w into the layer's latent page at the token's position, and
+//                     the last taps - 1 rows of h of every sequence into its ring.
+//   head_product      per head: q'_h = W_h^T q_h (the keys' up-projection taken into the query), or
+//                     o_h = W_h a_h times sigmoid(gate_h) (the values' up-projection after the sum).
+//   head_gate         o[t, h, :] *= sigmoid(gate[t, h])
+//   gated_add         x += y * sigmoid(g + b), optionally followed by the RMS norm of the new x
+//   xielu             a z^2 + z/2 above zero, (1/2 + b)(exp(z) - 1 - z) + z/2 below, a and b the
+//                     softplus of two learned numbers
+//
+// Rings are indexed by position, never by step: a decode step that is taken back and run again
+// at the same position reads what the step before it read.
+#include "common.cuh"
+
+G2B_DEFINE_LAST_ERROR
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// ---------------------------------------------------------------------------
+// embedding with a pair table and a norm
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void __launch_bounds__(256)
+embed_pair_norm_kernel(const TW *__restrict__ table, const TW *__restrict__ pairs,
+                       const int *__restrict__ ids, const int *__restrict__ tok_pos,
+                       const int *__restrict__ tok_seq, const int *__restrict__ seq_slots,
+                       const int *__restrict__ seq_meta, int *__restrict__ ring,
+                       const float *__restrict__ norm_w, float *__restrict__ out, int T, int H,
+                       int V, float scale, long long buckets, long long mul_prev,
+                       long long mul_cur, float eps) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  __shared__ int prev_s;
+  const int t = blockIdx.x;
+  const int b = tok_seq[t], pos = tok_pos[t];
+  int id = ids[t];
+  if (id < 0 || id >= V) id = 0;                     // the host validates ids; never read outside
+  if (threadIdx.x == 0) {
+    const bool first_of_step = (t == 0) || (tok_seq[t - 1] != b);
+    int prev = -1;
+    int *my_ring = ring + 2 * (size_t)seq_slots[b];
+    if (pos > 0) prev = first_of_step ? my_ring[(pos - 1) & 1] : ids[t - 1];
+    if (first_of_step) {
+      // this block alone reads and writes the slot's ring in this launch: the read above comes first
+      const int n = seq_meta ? seq_meta[4 * b + 1] : 1;
+      my_ring[(pos + n - 1) & 1] = ids[t + n - 1];
+    }
+    prev_s = prev;
+  }
+  __syncthreads();
+  const int prev = prev_s;
+  long long row = buckets;
+  if (prev >= 0) {
+    row = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+    if (row < 0) row += buckets;
+  }
+  const TW *e = table + (size_t)id * H;
+  const TW *g = pairs + (size_t)row * H;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float v = fmaf(to_f32(e[j]), scale, to_f32(g[j]));
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)H + eps);
+  float *o = out + (size_t)t * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float v = fmaf(to_f32(e[j]), scale, to_f32(g[j]));
+    o[j] = (v * inv) * norm_w[j];
+  }
+}
+
+extern "C" int g2b_embed_pair_norm(const void *table, const void *pairs, int table_dtype,
+                                   const int *ids, const int *tok_pos, const int *tok_seq,
+                                   const int *seq_slots, const int *seq_meta, int *ring,
+                                   const float *norm_w, float *out, int T, int H, int V,
+                                   float scale, long long buckets, long long mul_prev,
+                                   long long mul_cur, float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || V <= 0 || buckets <= 0) G2B_REFUSE("embed_pair_norm: bad sizes H=%d V=%d buckets=%lld", H, V, buckets);
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  if (table_dtype == G2B_F32)
+    g2b_launch(embed_pair_norm_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float *)table,
+               (const float *)pairs, ids, tok_pos, tok_seq, seq_slots, seq_meta, ring, norm_w, out, T, H,
+               V, scale, buckets, mul_prev, mul_cur, eps);
+  else if (table_dtype == G2B_BF16)
+    g2b_launch(embed_pair_norm_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16 *)table,
+               (const bf16 *)pairs, ids, tok_pos, tok_seq, seq_slots, seq_meta, ring, norm_w, out, T, H,
+               V, scale, buckets, mul_prev, mul_cur, eps);
+  else
+    G2B_REFUSE("embed_pair_norm: unknown table dtype %d", table_dtype);
+  return g2b_check_launch("embed_pair_norm");
+}
+
+// ---------------------------------------------------------------------------
+// causal convolution over time on each channel, added to its input
+// ---------------------------------------------------------------------------
+#define CANON_MAX_TAPS 16
+
+template <typename TA>
+__global__ void __launch_bounds__(256)
+canon_conv_kernel(const TA *__restrict__ h, const float *__restrict__ w, const TA *__restrict__ ring,
+                  const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
+                  const int *__restrict__ seq_slots, TA *__restrict__ out, int T, int H, int taps) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.y;
+  const int b = tok_seq[t], pos = tok_pos[t];
+  const TA *src[CANON_MAX_TAPS];                      // row that lies k steps back; nullptr: before the start
+  const TA *my_ring = ring + (size_t)seq_slots[b] * taps * H;
+#pragma unroll
+  for (int k = 0; k < CANON_MAX_TAPS; ++k) {
+    src[k] = nullptr;
+    if (k < taps && pos - k >= 0) {
+      if (t - k >= 0 && tok_seq[t - k] == b) src[k] = h + (size_t)(t - k) * H;
+      else src[k] = my_ring + (size_t)((pos - k) % taps) * H;
+    }
+  }
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= H) return;
+  const float own = to_f32(src[0][j]);
+  float acc = 0.f;
+#pragma unroll
+  for (int k = CANON_MAX_TAPS - 1; k >= 0; --k)        // oldest first: the order of the taps
+    if (k < taps && src[k]) acc = fmaf(w[(size_t)j * taps + (taps - 1 - k)], to_f32(src[k][j]), acc);
+  out[(size_t)t * H + j] = from_f32<TA>(own + acc);
+}
+
+extern "C" int g2b_canon_conv(const void *h, const float *w, const void *ring, int dtype,
+                              const int *tok_pos, const int *tok_seq, const int *seq_slots,
+                              void *out, int T, int H, int taps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (taps < 1 || taps > CANON_MAX_TAPS) G2B_REFUSE("canon_conv: %d taps outside 1..%d", taps, CANON_MAX_TAPS);
+  const int threads = H >= 256 ? 256 : 64;
+  const dim3 grid((H + threads - 1) / threads, T);
+  if (dtype == G2B_F32)
+    g2b_launch(canon_conv_kernel<float>, grid, dim3(threads), 0, stream, (const float *)h, w,
+               (const float *)ring, tok_pos, tok_seq, seq_slots, (float *)out, T, H, taps);
+  else if (dtype == G2B_BF16)
+    g2b_launch(canon_conv_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16 *)h, w,
+               (const bf16 *)ring, tok_pos, tok_seq, seq_slots, (bf16 *)out, T, H, taps);
+  else
+    G2B_REFUSE("canon_conv: unknown dtype %d", dtype);
+  return g2b_check_launch("canon_conv");
+}
+
+// ---------------------------------------------------------------------------
+// what a layer keeps of a token: its normed latent in the page of its position, and (the last
+// taps - 1 tokens of each sequence in the step) the row the convolution will need next
+// ---------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(128)
+latent_keep_kernel(const TA *__restrict__ d, int d_stride, int rank, const float *__restrict__ norm_w,
+                   float eps, TA *__restrict__ pages, const int *__restrict__ page_table, int P,
+                   int page_size, const TA *__restrict__ h, TA *__restrict__ ring, int H, int taps,
+                   const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
+                   const int *__restrict__ seq_slots, int T) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int b = tok_seq[t], pos = tok_pos[t];
+  if (d) {
+    const TA *dr = d + (size_t)t * d_stride;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) {
+      const float v = to_f32(dr[j]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)rank + eps);
+    const int page = page_table[(size_t)b * P + pos / page_size];
+    TA *row = pages + ((size_t)page * page_size + pos % page_size) * rank;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x)
+      row[j] = from_f32<TA>((to_f32(dr[j]) * inv) * norm_w[j]);
+  }
+  if (ring && taps > 1) {
+    // among the last taps - 1 tokens of its sequence in this step?
+    const int ahead = t + taps - 1;
+    if (ahead >= T || tok_seq[ahead] != b) {
+      TA *row = ring + ((size_t)seq_slots[b] * taps + pos % taps) * H;
+      const TA *hr = h + (size_t)t * H;
+      for (int j = threadIdx.x; j < H; j += blockDim.x) row[j] = hr[j];
+    }
+  }
+}
+
+extern "C" int g2b_latent_keep(const void *d, int d_stride, int rank, const float *norm_w, float eps,
+                               void *pages, const int *page_table, int P, int page_size,
+                               const void *h, void *ring, int H, int taps, int dtype,
+                               const int *tok_pos, const int *tok_seq, const int *seq_slots, int T,
+                               cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (d && (rank <= 0 || page_size <= 0)) G2B_REFUSE("latent_keep: bad sizes rank=%d page=%d", rank, page_size);
+  if (dtype == G2B_F32)
+    g2b_launch(latent_keep_kernel<float>, dim3(T), dim3(128), 0, stream, (const float *)d, d_stride, rank,
+               norm_w, eps, (float *)pages, page_table, P, page_size, (const float *)h, (float *)ring, H,
+               taps, tok_pos, tok_seq, seq_slots, T);
+  else if (dtype == G2B_BF16)
+    g2b_launch(latent_keep_kernel<bf16>, dim3(T), dim3(128), 0, stream, (const bf16 *)d, d_stride, rank,
+               norm_w, eps, (bf16 *)pages, page_table, P, page_size, (const bf16 *)h, (bf16 *)ring, H,
+               taps, tok_pos, tok_seq, seq_slots, T);
+  else
+    G2B_REFUSE("latent_keep: unknown dtype %d", dtype);
+  return g2b_check_launch("latent_keep");
+}
+
+// ---------------------------------------------------------------------------
+// products with one small matrix per head.  W [heads * n, r] (rows of head h: h*n .. h*n+n-1).
+//   absorb: out[t, h, 0..r)  = sum_i W[h*n + i, :] * in[t, h, i]        (W_h^T applied; in has n per head)
+//   expand: out[t, h, 0..n)  = W[h*n + i, :] . in[t, h, :], times sigmoid(gate[t, h]) when gate
+// One block per (head, tile of HP_ROWS tokens); the sum over the inner index always runs in
+// the same order, so a token's result does not depend on its tile.
+// ---------------------------------------------------------------------------
+#define HP_ROWS 8
+#define HP_THREADS 256
+
+template <typename TA>
+__global__ void __launch_bounds__(HP_THREADS)
+head_absorb_kernel(const TA *__restrict__ in, int in_stride, const TA *__restrict__ W,
+                   TA *__restrict__ out, int out_stride, int T, int heads, int n, int r) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float hp_smem[];                  // [HP_ROWS][n]
+  const int h = blockIdx.x, t0 = blockIdx.y * HP_ROWS;
+  const int rows = min(HP_ROWS, T - t0);
+  for (int i = threadIdx.x; i < HP_ROWS * n; i += blockDim.x) {
+    const int m = i / n, k = i % n;
+    hp_smem[i] = m < rows ? to_f32(in[(size_t)(t0 + m) * in_stride + (size_t)h * n + k]) : 0.f;
+  }
+  __syncthreads();
+  const TA *Wh = W + (size_t)h * n * r;
+  for (int c = threadIdx.x; c < r; c += blockDim.x) {
+    float acc[HP_ROWS];
+#pragma unroll
+    for (int m = 0; m < HP_ROWS; ++m) acc[m] = 0.f;
+    for (int k = 0; k < n; ++k) {
+      const float w = to_f32(Wh[(size_t)k * r + c]);
+#pragma unroll
+      for (int m = 0; m < HP_ROWS; ++m) acc[m] = fmaf(w, hp_smem[m * n + k], acc[m]);
+    }
+#pragma unroll
+    for (int m = 0; m < HP_ROWS; ++m)
+      if (m < rows) out[(size_t)(t0 + m) * out_stride + (size_t)h * r + c] = from_f32<TA>(acc[m]);
+  }
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(HP_THREADS)
+head_expand_kernel(const TA *__restrict__ in, int in_stride, const TA *__restrict__ W,
+                   const TA *__restrict__ gate, int gate_stride, TA *__restrict__ out,
+                   int out_stride, int T, int heads, int n, int r) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float hp_smem[];                  // [HP_ROWS][r]
+  const int h = blockIdx.x, t0 = blockIdx.y * HP_ROWS;
+  const int rows = min(HP_ROWS, T - t0);
+  for (int i = threadIdx.x; i < HP_ROWS * r; i += blockDim.x) {
+    const int m = i / r, k = i % r;
+    hp_smem[i] = m < rows ? to_f32(in[(size_t)(t0 + m) * in_stride + (size_t)h * r + k]) : 0.f;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  for (int i = warp; i < n; i += n_warps) {
+    const TA *wr = W + ((size_t)h * n + i) * r;
+    float acc[HP_ROWS];
+#pragma unroll
+    for (int m = 0; m < HP_ROWS; ++m) acc[m] = 0.f;
+    for (int k = lane; k < r; k += 32) {
+      const float w = to_f32(wr[k]);
+#pragma unroll
+      for (int m = 0; m < HP_ROWS; ++m) acc[m] = fmaf(w, hp_smem[m * r + k], acc[m]);
+    }
+#pragma unroll
+    for (int m = 0; m < HP_ROWS; ++m) acc[m] = warp_sum(acc[m]);
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < HP_ROWS; ++m)
+        if (m < rows) {
+          float v = acc[m];
+          if (gate) v *= sigmoid_f(to_f32(gate[(size_t)(t0 + m) * gate_stride + h]));
+          out[(size_t)(t0 + m) * out_stride + (size_t)h * n + i] = from_f32<TA>(v);
+        }
+    }
+  }
+}
+
+extern "C" int g2b_head_product(const void *in, int in_stride, const void *W, const void *gate,
+                                int gate_stride, void *out, int out_stride, int T, int heads, int n,
+                                int r, int expand, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (heads <= 0 || n <= 0 || r <= 0) G2B_REFUSE("head_product: bad sizes heads=%d n=%d r=%d", heads, n, r);
+  const size_t smem = sizeof(float) * HP_ROWS * (size_t)(expand ? r : n);
+  if (smem > 48 * 1024) G2B_REFUSE("head_product: %d values per head and token are more than fit", expand ? r : n);
+  const dim3 grid(heads, (T + HP_ROWS - 1) / HP_ROWS);
+  if (dtype == G2B_F32) {
+    if (expand)
+      g2b_launch(head_expand_kernel<float>, grid, dim3(HP_THREADS), smem, stream, (const float *)in, in_stride,
+                 (const float *)W, (const float *)gate, gate_stride, (float *)out, out_stride, T, heads, n, r);
+    else
+      g2b_launch(head_absorb_kernel<float>, grid, dim3(HP_THREADS), smem, stream, (const float *)in, in_stride,
+                 (const float *)W, (float *)out, out_stride, T, heads, n, r);
+  } else if (dtype == G2B_BF16) {
+    if (expand)
+      g2b_launch(head_expand_kernel<bf16>, grid, dim3(HP_THREADS), smem, stream, (const bf16 *)in, in_stride,
+                 (const bf16 *)W, (const bf16 *)gate, gate_stride, (bf16 *)out, out_stride, T, heads, n, r);
+    else
+      g2b_launch(head_absorb_kernel<bf16>, grid, dim3(HP_THREADS), smem, stream, (const bf16 *)in, in_stride,
+                 (const bf16 *)W, (bf16 *)out, out_stride, T, heads, n, r);
+  } else {
+    G2B_REFUSE("head_product: unknown dtype %d", dtype);
+  }
+  return g2b_check_launch("head_product");
+}
+
+// o[t, h, :] *= sigmoid(gate[t, h]); o [T, heads * n] contiguous
+template <typename TA>
+__global__ void head_gate_kernel(TA *__restrict__ o, const TA *__restrict__ gate, int gate_stride,
+                                 int heads, int n, long long total) {
+  pdl_launch();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long th = i / n;                          // token * heads + head
+  const float g = to_f32(gate[(th / heads) * gate_stride + th % heads]);
+  o[i] = from_f32<TA>(to_f32(o[i]) * sigmoid_f(g));
+}
+
+extern "C" int g2b_head_gate(void *o, const void *gate, int gate_stride, int T, int heads, int n,
+                             int dtype, cudaStream_t stream) {
+  const long long total = (long long)T * heads * n;
+  if (total <= 0) return 0;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == G2B_F32)
+    g2b_launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float *)o, (const float *)gate,
+               gate_stride, heads, n, total);
+  else if (dtype == G2B_BF16)
+    g2b_launch(head_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16 *)o, (const bf16 *)gate,
+               gate_stride, heads, n, total);
+  else
+    G2B_REFUSE("head_gate: unknown dtype %d", dtype);
+  return g2b_check_launch("head_gate");
+}
+
+// ---------------------------------------------------------------------------
+// x += y * sigmoid(g + b); then, when `normed` is given, normed = x / sqrt(mean(x^2) + eps) * w
+// (the norm in front of the next sublayer).  One block per row.
+// ---------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(256)
+gated_add_kernel(float *__restrict__ x, const float *__restrict__ y, const TA *__restrict__ g,
+                 int g_stride, const float *__restrict__ bias, int H, const float *__restrict__ norm_w,
+                 float eps, TA *__restrict__ normed) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  float *xr = x + (size_t)t * H;
+  const float *yr = y + (size_t)t * H;
+  const TA *gr = g + (size_t)t * g_stride;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float z = to_f32(gr[j]) + (bias ? bias[j] : 0.f);
+    const float v = fmaf(yr[j], sigmoid_f(z), xr[j]);
+    xr[j] = v;
+    ss = fmaf(v, v, ss);
+  }
+  if (!normed) return;
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)H + eps);
+  TA *o = normed + (size_t)t * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x)   // a thread reads back what it wrote itself
+    o[j] = from_f32<TA>((xr[j] * inv) * (norm_w ? norm_w[j] : 1.f));
+}
+
+extern "C" int g2b_gated_add(float *x, const float *y, const void *g, int g_stride, const float *bias,
+                             int T, int H, const float *norm_w, float eps, void *normed, int dtype,
+                             cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  if (dtype == G2B_F32)
+    g2b_launch(gated_add_kernel<float>, dim3(T), dim3(threads), 0, stream, x, y, (const float *)g, g_stride,
+               bias, H, norm_w, eps, (float *)normed);
+  else if (dtype == G2B_BF16)
+    g2b_launch(gated_add_kernel<bf16>, dim3(T), dim3(threads), 0, stream, x, y, (const bf16 *)g, g_stride,
+               bias, H, norm_w, eps, (bf16 *)normed);
+  else
+    G2B_REFUSE("gated_add: unknown dtype %d", dtype);
+  return g2b_check_launch("gated_add");
+}
+
+// ---------------------------------------------------------------------------
+// xIELU on the first F columns of a [T, stride] buffer
+// ---------------------------------------------------------------------------
+template <typename TA>
+__global__ void xielu_kernel(const TA *__restrict__ in, int in_stride, const float *__restrict__ pq,
+                             TA *__restrict__ out, int F, long long total) {
+  pdl_launch();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float a = softplus_f(pq[0]), bq = 0.5f + softplus_f(pq[1]);
+  const float z = to_f32(in[(i / F) * in_stride + i % F]);
+  const float v = z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(bq, expm1f(z) - z, 0.5f * z);
+  out[i] = from_f32<TA>(v);
+}
+
+extern "C" int g2b_xielu(const void *in, int in_stride, const float *pq, void *out, int T, int F,
+                         int dtype, cudaStream_t stream) {
+  const long long total = (long long)T * F;
+  if (total <= 0) return 0;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == G2B_F32)
+    g2b_launch(xielu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *)in, in_stride, pq,
+               (float *)out, F, total);
+  else if (dtype == G2B_BF16)
+    g2b_launch(xielu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16 *)in, in_stride, pq,
+               (bf16 *)out, F, total);
+  else
+    G2B_REFUSE("xielu: unknown dtype %d", dtype);
+  return g2b_check_launch("xielu");
+}

@@ -82,7 +82,8 @@ class DecodeRunner:
             n_tokens=B, n_seqs=B, tok_ids=self.tok_ids, tok_pos=self.tok_pos, tok_seq=self.tok_seq,
             page_table=self.page_table, page_size=engine.cache.page_size,
             workspace=engine.workspace, dtype=engine.model.dtype, q_lens=[1] * B,
-            past_lens=[0] * B, slots=[0] * B, max_kv_len=P * engine.cache.page_size)
+            past_lens=[0] * B, slots=[0] * B, max_kv_len=P * engine.cache.page_size,
+            seq_slots=self.slots)
         # what a session needs to talk to the host, kept here so that a new session of a known
         # shape allocates nothing (pinned memory is slow to get)
         self.pinned_in = torch.empty(B, dtype=torch.int32, pin_memory=True)
@@ -203,8 +204,10 @@ class DecodeSession:
         self.use_graph = use_graph and engine.model.graph_safe
         self.eager_steps = max(1, DecodeRunner.EAGER_STEPS if eager_steps is None else int(eager_steps))
         # a step launched ahead can be taken back only if all it stored is stored by position
+        # (a fixed-size state qualifies when it is a ring indexed by position: ``StateNeed.by_position``)
         self._may_run_ahead = self._sample_in_graph and all(
-            isinstance(g["need"], KVNeed) for g in engine.cache.groups.values())
+            isinstance(g["need"], KVNeed) or getattr(g["need"], "by_position", False)
+            for g in engine.cache.groups.values())
         self._ahead: Optional[list] = None      # tokens, row by row, fed to the step launched ahead, if any
         self._since_check = 0
 

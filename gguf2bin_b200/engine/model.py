@@ -126,8 +126,18 @@ class Model:
     def cache_needs(self) -> list:
         """The need of each schedule position: what its layer asks for, or None when the
         position borrows another position's storage or its layer stores nothing."""
-        return [self.blocks[e.layer].cache_need() if e.cache_of is None else None
-                for e in self.spec.schedule]
+        out = []
+        for e in self.spec.schedule:
+            need = self.blocks[e.layer].cache_need()
+            if e.cache_of is not None:
+                # a borrower keeps what it states under names of its own (a block whose mixer
+                # shares another layer's storage states no need for the mixer)
+                need = {k: v for k, v in need.items() if v is not None} or None \
+                    if isinstance(need, dict) else None
+            out.append(need)
+        if hasattr(self.embedding, "cache_need"):
+            out.append(self.embedding.cache_need())
+        return out
 
     def new_cache(self, max_tokens: int, max_seqs: Optional[int] = None) -> Cache:
         return Cache(self.cache_needs(), max_tokens, self.dtype, self.device, max_seqs)
@@ -170,9 +180,14 @@ class Model:
         ws = ctx.workspace
         ctx.step_cache.clear()                     # per-step tables are rebuilt from this step's tokens
         x = ws.buffer("stream", (ctx.n_tokens, self.hidden), torch.float32)
-        self.embedding.forward(ctx.tok_ids[:ctx.n_tokens], x, ctx)
+        if hasattr(self.embedding, "cache_need"):
+            # an embedding that keeps something per sequence (the previous token, say) has the
+            # storage of one more position behind the schedule's
+            self.embedding.forward(ctx.tok_ids[:ctx.n_tokens], x, ctx, cache.view(len(self.spec.schedule)))
+        else:
+            self.embedding.forward(ctx.tok_ids[:ctx.n_tokens], x, ctx)
         for position, entry in enumerate(self.spec.schedule):
-            self.blocks[entry.layer].forward(x, ctx, cache.view(self.spec.cache_owner(position)))
+            self.blocks[entry.layer].forward(x, ctx, cache.view_for(position, self.spec.cache_owner(position)))
         if n_want == 0:
             return None
         logits = logits_out if logits_out is not None else \

@@ -181,8 +181,8 @@ class Engine:
         tiles = tiles + wide
         n_tiles = len(tiles)
         # layout: tiles[n_tiles*4] tok_ids[T] tok_pos[T] tok_seq[T] want[n_want] seq_meta[B*4]
-        #         page_table[B*P]   (the tiles come first: the kernel reads them 16 bytes at a time)
-        total = 4 * n_tiles + 3 * T + n_want + 4 * B + B * P
+        #         page_table[B*P] seq_slots[B]   (the tiles come first: the kernel reads them 16 bytes at a time)
+        total = 4 * n_tiles + 3 * T + n_want + 4 * B + B * P + B
         if total > self._meta_cap:
             self._meta_cap = max(2 * total, 1024)
             self._meta_dev = torch.empty(self._meta_cap, dtype=torch.int32, device=self.device)
@@ -193,6 +193,7 @@ class Engine:
         o_meta = o_want + n_want
         host[:4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
         o_pt = o_meta + 4 * B
+        o_slots = o_pt + B * P
         t0 = w0 = 0
         for b, e in enumerate(entries):
             n = q_lens[b]
@@ -206,6 +207,7 @@ class Engine:
             row = host[o_pt + b * P:o_pt + (b + 1) * P]
             row[:len(e.seq.pages)] = e.seq.pages
             row[len(e.seq.pages):] = 0
+            host[o_slots + b] = e.seq.slot
             t0 += n
         dev = self._meta_dev
         dev[:total].copy_(self._meta_host[:total], non_blocking=True)
@@ -215,7 +217,7 @@ class Engine:
             page_size=self.cache.page_size, workspace=self.workspace, dtype=self.model.dtype,
             q_lens=q_lens, past_lens=past, slots=[e.seq.slot for e in entries],
             max_kv_len=max(p + n for p, n in zip(past, q_lens)),
-            seq_meta=dev[o_meta:o_meta + 4 * B].view(B, 4),
+            seq_meta=dev[o_meta:o_meta + 4 * B].view(B, 4), seq_slots=dev[o_slots:o_slots + B],
             attn_tiles=dev[:4 * n_narrow].view(n_narrow, 4), n_attn_tiles=n_narrow,
             attn_tiles_wide=dev[4 * n_narrow:4 * n_tiles].view(n_tiles - n_narrow, 4),
             n_attn_tiles_wide=n_tiles - n_narrow)

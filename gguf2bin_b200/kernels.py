@@ -217,6 +217,119 @@ def rewind_step(tok_pos: torch.Tensor, n: int, seq_state: Optional[torch.Tensor]
 
 
 # ---------------------------------------------------------------------------
+# stream_ops.cu: the parts around the products of a gated layer with a latent cache
+# ---------------------------------------------------------------------------
+def embed_pair_norm(table, pairs, ids, ctx, ring, norm_w, eps, scale, buckets, mul_prev, mul_cur,
+                    out) -> None:
+    """out[t] = rmsnorm(table[ids[t]] * scale + pairs[row_t]) * norm_w as float32, row_t a hash of
+    the previous and the current token (``buckets`` for a sequence's first token).  ``ring``
+    int32 [slots, 2]: the last token of every sequence, by position parity."""
+    from ctypes import c_longlong
+    _need(ids, torch.int32, "ids")
+    _need(out, torch.float32, "out")
+    _need(ring, torch.int32, "ring")
+    _need(norm_w, torch.float32, "norm weight")
+    if pairs.dtype != table.dtype or pairs.shape[1] != table.shape[1] or pairs.shape[0] != buckets + 1:
+        raise KernelError("embed_pair_norm: the pair table must be [buckets + 1, width] in the table's dtype")
+    V, H = table.shape
+    f = _fn("stream_ops.cu", "g2b_embed_pair_norm",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong,
+             c_float, c_void_p])
+    _call(f, _ptr(table), _ptr(pairs), _code(table.dtype), _ptr(ids), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
+          _ptr(ctx.seq_slots), _ptr(ctx.seq_meta), _ptr(ring), _ptr(norm_w), _ptr(out), out.shape[0], H, V,
+          float(scale), int(buckets), int(mul_prev), int(mul_cur), float(eps), _stream())
+
+
+def canon_conv(h, w32, ring, ctx, out) -> None:
+    """out = h + causal convolution of h over time per channel; w32 float32 [width, taps];
+    ``ring`` [slots, taps, width]: the rows before the step, by position mod taps."""
+    _need(w32, torch.float32, "convolution weight")
+    if ring.dtype != h.dtype or out.dtype != h.dtype:
+        raise KernelError("canon_conv: input, output and ring must have one dtype")
+    T, H = h.shape
+    f = _fn("stream_ops.cu", "g2b_canon_conv",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_void_p])
+    _call(f, _ptr(h), _ptr(w32), _ptr(ring), _code(h.dtype), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
+          _ptr(ctx.seq_slots), _ptr(out), T, H, w32.shape[1], _stream())
+
+
+def latent_keep(d, norm_w, eps, pages, h, ring, taps, ctx) -> None:
+    """Writes rmsnorm(d) * norm_w (d [T, rank], a view with any row stride; None: nothing) into
+    the latent pages at the tokens' positions, and the last ``taps - 1`` rows of ``h`` of every
+    sequence into ``ring`` (None: nothing)."""
+    f = _fn("stream_ops.cu", "g2b_latent_keep",
+            [c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    ref = d if d is not None else h
+    if d is not None:
+        _need(norm_w, torch.float32, "latent norm weight")
+        if d.stride(1) != 1 or pages.dtype != d.dtype:
+            raise KernelError("latent_keep: the latents must be rows of the cache's dtype")
+    if ring is not None and (ring.dtype != h.dtype or not h.is_contiguous()):
+        raise KernelError("latent_keep: ring and rows must have one dtype")
+    _call(f, _ptr(d), d.stride(0) if d is not None else 0, d.shape[1] if d is not None else 0,
+          _ptr(norm_w), float(eps), _ptr(pages), _ptr(ctx.page_table), ctx.page_table.shape[1],
+          ctx.page_size, _ptr(h) if ring is not None else None, _ptr(ring),
+          h.shape[1] if ring is not None else 0, int(taps), _code(ref.dtype), _ptr(ctx.tok_pos),
+          _ptr(ctx.tok_seq), _ptr(ctx.seq_slots), ref.shape[0], _stream())
+
+
+def head_product(x, w, out, heads: int, expand: bool, gate=None) -> None:
+    """One small matrix per head, w [heads * n, r].  ``expand`` False: out[t, h] = w_h^T x[t, h]
+    (x has n values per head, out r); True: out[t, h] = w_h x[t, h] (x has r per head, out n),
+    times sigmoid(gate[t, h]) when ``gate`` [T, heads] is given.  Views with row strides are taken."""
+    n, r = w.shape[0] // heads, w.shape[1]
+    if x.dtype != w.dtype or out.dtype != w.dtype or not w.is_contiguous():
+        raise KernelError("head_product: x, w and out must have one dtype, w contiguous")
+    if x.stride(1) != 1 or out.stride(1) != 1 or (gate is not None and (gate.stride(1) != 1 or gate.dtype != x.dtype)):
+        raise KernelError("head_product: innermost strides must be 1")
+    f = _fn("stream_ops.cu", "g2b_head_product",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_void_p])
+    _call(f, _ptr(x), x.stride(0), _ptr(w), _ptr(gate), gate.stride(0) if gate is not None else 0,
+          _ptr(out), out.stride(0), x.shape[0], heads, n, r, 1 if expand else 0, _code(x.dtype), _stream())
+
+
+def head_gate(o, gate, heads: int) -> None:
+    """o[t, h, :] *= sigmoid(gate[t, h]) in place; o [T, heads * n] contiguous."""
+    if not o.is_contiguous() or gate.dtype != o.dtype or gate.stride(1) != 1:
+        raise KernelError("head_gate: o contiguous, gate of o's dtype")
+    f = _fn("stream_ops.cu", "g2b_head_gate", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _call(f, _ptr(o), _ptr(gate), gate.stride(0), o.shape[0], heads, o.shape[1] // heads, _code(o.dtype), _stream())
+
+
+def gated_add(x32, y32, g, bias, norm_w=None, eps: float = 0.0, normed=None) -> None:
+    """x32 += y32 * sigmoid(g + bias) row by row (g a view with any row stride); with ``normed``
+    also normed = rmsnorm(x32) * norm_w of the new rows."""
+    _need(x32, torch.float32, "x")
+    _need(y32, torch.float32, "y")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    if g.stride(1) != 1 or (normed is not None and (normed.dtype != g.dtype or not normed.is_contiguous())):
+        raise KernelError("gated_add: gate rows must be dense, normed of the gate's dtype")
+    if norm_w is not None:
+        _need(norm_w, torch.float32, "norm weight")
+    T, H = x32.shape
+    f = _fn("stream_ops.cu", "g2b_gated_add",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p,
+             c_int, c_void_p])
+    _call(f, _ptr(x32), _ptr(y32), _ptr(g), g.stride(0), _ptr(bias), T, H, _ptr(norm_w), float(eps),
+          _ptr(normed), _code(g.dtype), _stream())
+
+
+def xielu(z, pq32, out) -> None:
+    """out = a z^2 + z/2 for z > 0, (1/2 + b)(exp(z) - 1 - z) + z/2 otherwise, a = softplus(pq[0]),
+    b = softplus(pq[1]); z a view [T, F] with any row stride, out [T, F] contiguous."""
+    _need(pq32, torch.float32, "activation parameters")
+    if z.stride(1) != 1 or out.dtype != z.dtype or not out.is_contiguous():
+        raise KernelError("xielu: dense rows of one dtype")
+    f = _fn("stream_ops.cu", "g2b_xielu", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _call(f, _ptr(z), z.stride(0), _ptr(pq32), _ptr(out), z.shape[0], z.shape[1], _code(z.dtype), _stream())
+
+
+# ---------------------------------------------------------------------------
 # random_init.cu
 # ---------------------------------------------------------------------------
 def philox_normal(out: torch.Tensor, seed: int, tensor_index: int, scale_vector: bool, std: float) -> None:
@@ -295,29 +408,33 @@ def attention_notices(what: str, head_dim: int, page_size: int, compute_dtype: t
 # attention
 # ---------------------------------------------------------------------------
 def attn_generic(q, out, cache_pages, tok_pos, tok_seq, page_table, n_heads, n_kv_heads,
-                 head_dim, page_size, window, scale) -> None:
+                 head_dim, page_size, window, scale, sink=None, planes: int = 2) -> None:
     """Causal attention of every token of the step over its sequence's cache pages,
-    32-bit arithmetic; q, out [T, n_heads*head_dim]."""
+    32-bit arithmetic; q, out [T, n_heads*head_dim].  ``sink`` (float32 [n_heads]): one more
+    term exp(sink_h) in each head's softmax denominator.  ``planes`` = 1: the pages hold one
+    panel per kv head that is read as keys and as values."""
     f = _fn("attn_generic.cu", "g2b_attn_generic",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p])
     if q.dtype != cache_pages.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, out and the cache must have one dtype")
+    if sink is not None:
+        _need(sink, torch.float32, "sink")
     _call(f, _ptr(q), _ptr(out), _code(q.dtype), _ptr(cache_pages), _ptr(tok_pos), _ptr(tok_seq),
           _ptr(page_table), page_table.shape[1], q.shape[0], n_heads, n_kv_heads, head_dim,
-          page_size, window, scale, _stream())
+          page_size, window, scale, _ptr(sink), planes, _stream())
 
 
 def attention(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-              scale) -> None:
+              scale, sink=None, planes: int = 2) -> None:
     """Attention of a step: the tensor-core kernels when they take the case, else the
     32-bit kernel."""
     if q.dtype == torch.bfloat16:
         if (_bf16 or _bf16_mod()).attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim,
-                                       page_size, window, scale):
+                                       page_size, window, scale, sink, planes):
             return
     attn_generic(q, out, cache_pages, ctx.tok_pos, ctx.tok_seq, ctx.page_table, n_heads,
-                 n_kv_heads, head_dim, page_size, window, scale)
+                 n_kv_heads, head_dim, page_size, window, scale, sink, planes)
 
 
 def normed_product(x32, eps, w, out, gate_block=None) -> bool:

@@ -283,8 +283,10 @@ def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, bl
 
 
 def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                   scale) -> bool:
+                   scale, sink=None, planes: int = 2) -> bool:
     if head_dim not in FAST_HEAD_SIZES or page_size != 64 or cache_pages.dtype != torch.bfloat16:
+        return False
+    if sink is not None or planes != 2:
         return False
     if ctx.all_single:
         attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale)

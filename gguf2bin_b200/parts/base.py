@@ -53,7 +53,8 @@ class StepContext:
     slots: list = field(default_factory=list)        # slot of each sequence
     max_kv_len: int = 0                              # longest sequence after this step (a replayed decode step: its upper bound)
     kv_len_hint: int = 0                             # where max_kv_len is an upper bound: the longest sequence as of now (0: unknown)
-    seq_meta: Optional[torch.Tensor] = None          # [B,4] int32: q_start, q_len, past, slot
+    seq_meta: Optional[torch.Tensor] = None          # [B,4] int32: q_start, q_len, past, slot (None: one token per sequence)
+    seq_slots: Optional[torch.Tensor] = None         # [B] int32: slot of each sequence, for parts that keep a state per slot
     attn_tiles: Optional[torch.Tensor] = None        # [n,4] int32: sequence, first token, rows, position
     n_attn_tiles: int = 0                            # of row 0; tiles of ATTN_TILE_ROWS query rows
     attn_tiles_wide: Optional[torch.Tensor] = None   # the same with ATTN_WIDE_TILE_ROWS rows (tcgen05 kernel)

@@ -1,10 +1,16 @@
 """Block arrangements.  ``prenorm``: x += mixer(norm(x)); x += feed_forward(norm(x)), the
-residual stream kept in float32 (src/l5_model.c:494-597 of AnonymoDGH/gguf2bin)."""
+residual stream kept in float32 (src/l5_model.c:494-597 of AnonymoDGH/gguf2bin).
+``gated_prenorm``: the same with each sublayer's result scaled by a learned gate, an optional
+short convolution over time in front of the mixer, and an optional feed-forward."""
 from __future__ import annotations
 
 import torch
 
+from .. import kernels
+from ..cache.storage import StateNeed
 from ..config.specs import LayerSpec
+from ..weights.loader import Expected
+from .norms import RMSNorm
 from .registry import (feed_forward_class, mixer_class, norm_class, register_block)
 
 
@@ -81,4 +87,141 @@ class PreNormBlock:
             self.feed_forward.forward(h, ctx, x32)
 
 
+class GatedPreNormBlock:
+    """``gated_prenorm``: h = norm(x); x += mixer(h + conv(h)) * sigmoid(G1 h + b1);
+    h = norm(x); x += feed_forward(h) * sigmoid(G2 h + b2).
+
+    Each sublayer's result is scaled, element by element, by a gate that is a linear function of
+    the sublayer's normed input.  ``conv_taps`` > 0: what the mixer reads is its normed input plus
+    a causal convolution of it over time, one filter of that many taps per channel (the gate
+    still reads the input as normed).  The last ``conv_taps - 1`` normed rows of a sequence are
+    the block's own state: a ring of ``conv_taps`` rows per slot, indexed by position.  A layer
+    may have no feed-forward.  Mixers and feed-forwards that offer ``forward_into`` store their
+    result for the gate; any other part of the library adds into a cleared buffer instead.
+    """
+
+    def __init__(self, layer: LayerSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.names = dict(layer.block["names"])
+        self.hidden, self.dtype = int(hidden_size), dtype
+        self.taps = int(layer.block.get("conv_taps") or 0)
+        ffn_norm = layer.ffn_norm or layer.norm
+        self.mixer_norm = norm_class(layer.norm)(layer.norm, hidden_size, dtype, device)
+        self.mixer = mixer_class(layer.mixer)(layer.mixer, hidden_size, dtype, device)
+        self.feed_forward = self.ffn_norm = None
+        if layer.feed_forward is not None:
+            self.ffn_norm = norm_class(ffn_norm)(ffn_norm, hidden_size, dtype, device)
+            self.feed_forward = feed_forward_class(layer.feed_forward)(layer.feed_forward, hidden_size,
+                                                                       dtype, device)
+        self.w_conv = self.g1 = self.b1 = self.g2 = self.b2 = None
+        self._g2_rides = False
+
+    @classmethod
+    def expected(cls, layer: LayerSpec, hidden_size: int) -> dict:
+        names = dict(layer.block["names"])
+        H = int(hidden_size)
+        out = {}
+        out.update(norm_class(layer.norm).expected(layer.norm, H, names["mixer_norm"]))
+        out.update(mixer_class(layer.mixer).expected(layer.mixer, H))
+        out[names["mixer_gate"]] = Expected((H, H))
+        out[names["mixer_gate_bias"]] = Expected((H,))
+        taps = int(layer.block.get("conv_taps") or 0)
+        if taps:
+            out[names["conv"]] = Expected((H, taps))
+        if layer.feed_forward is not None:
+            ffn_norm = layer.ffn_norm or layer.norm
+            out.update(norm_class(ffn_norm).expected(ffn_norm, H, names["ffn_norm"]))
+            out.update(feed_forward_class(layer.feed_forward).expected(layer.feed_forward, H))
+            out[names["ffn_gate"]] = Expected((H, H))
+            out[names["ffn_gate_bias"]] = Expected((H,))
+        return out
+
+    def bind(self, tensors: dict) -> None:
+        n = self.names
+        self.mixer_norm.bind(tensors[n["mixer_norm"]])
+        self.mixer.bind(tensors)
+        self.g1 = tensors[n["mixer_gate"]].contiguous()
+        self.b1 = tensors[n["mixer_gate_bias"]].to(torch.float32).contiguous()
+        if self.taps:
+            self.w_conv = tensors[n["conv"]].to(torch.float32).contiguous()
+        if self.feed_forward is not None:
+            self.ffn_norm.bind(tensors[n["ffn_norm"]])
+            self.feed_forward.bind(tensors)
+            self.g2 = tensors[n["ffn_gate"]].contiguous()
+            self.b2 = tensors[n["ffn_gate_bias"]].to(torch.float32).contiguous()
+            # the gate's matrix reads what the feed-forward's first matrix reads: one product
+            take = getattr(self.feed_forward, "take_along", None)
+            self._g2_rides = bool(take is not None and take(self.g2))
+
+    def cache_need(self):
+        need = {"mixer": self.mixer.cache_need()}
+        if self.taps > 1:
+            need["conv"] = StateNeed((self.taps, self.hidden), self.dtype, by_position=True)
+        return need
+
+    def parts(self) -> tuple:
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+                     if p is not None)
+
+    def weights(self):
+        for part in self.parts():
+            yield from getattr(part, "weights", tuple)()
+        for t in (self.w_conv, self.g1, self.b1, self.b2) + (() if self._g2_rides else (self.g2,)):
+            if t is not None:
+                yield t
+
+    def notices(self) -> list:
+        out = [line for part in self.parts() for line in getattr(part, "notices", list)()]
+        return out + kernels.product_notices("residual gate", self.g1, self.dtype)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", False) for part in self.parts())
+
+    def forward(self, x32: torch.Tensor, ctx, cache_view) -> None:
+        T, H, ws = x32.shape[0], self.hidden, ctx.workspace
+        view = cache_view or {}
+        h = ws.buffer("gated.normed", (T, H), self.dtype)
+        self.mixer_norm.forward(x32, h)
+        u, keep = h, None
+        if self.taps:
+            ring = view["conv"].states if self.taps > 1 else h      # one tap: nothing before the token
+            u = ws.buffer("gated.conv", (T, H), self.dtype)
+            kernels.canon_conv(h, self.w_conv, ring, ctx, u)
+            if self.taps > 1:
+                keep = (h, ring, self.taps)
+        gate = ws.buffer("gated.gate", (T, H), self.dtype)
+        kernels.linear(h, self.g1, gate)
+        y = ws.buffer("gated.result", (T, H), torch.float32)
+        if hasattr(self.mixer, "forward_into"):
+            self.mixer.forward_into(u, ctx, view.get("mixer"), y, keep=keep)
+        else:
+            if keep is not None:
+                kernels.latent_keep(None, None, 0.0, None, h, keep[1], self.taps, ctx)
+            y.zero_()
+            self.mixer.forward(u, ctx, view.get("mixer"), y)
+        if self.feed_forward is None:
+            kernels.gated_add(x32, y, gate, self.b1)
+            return
+        # the feed-forward's norm rides on the gated addition when it is a plain RMS norm
+        eps = getattr(self.ffn_norm, "eps", None)
+        w2 = getattr(self.ffn_norm, "weight", None)
+        if isinstance(self.ffn_norm, RMSNorm) and w2 is not None:
+            kernels.gated_add(x32, y, gate, self.b1, w2, eps, h)
+        else:
+            kernels.gated_add(x32, y, gate, self.b1)
+            self.ffn_norm.forward(x32, h)
+        ff = self.feed_forward
+        if hasattr(ff, "forward_into"):
+            ff.forward_into(h, ctx, y)
+        else:
+            y.zero_()
+            ff.forward(h, ctx, y)
+        if self._g2_rides:
+            gate = ff.side_out
+        else:
+            kernels.linear(h, self.g2, gate)
+        kernels.gated_add(x32, y, gate, self.b2)
+
+
 register_block("prenorm", PreNormBlock)
+register_block("gated_prenorm", GatedPreNormBlock)

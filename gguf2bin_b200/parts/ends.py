@@ -82,5 +82,48 @@ class LMHead:
         kernels.linear(h, self.matrix, logits32)
 
 
+class PairEmbedding:
+    """``pair_embedding``: x_t = table[id_t] * scale + pairs[row_t], then an RMS norm with a weight.
+    row_t = (id_{t-1} * mul_prev + id_t * mul_cur) mod buckets: a second, hashed table addressed by
+    the previous and the current token; a sequence's first token takes the row behind the
+    buckets (``pairs`` has ``buckets + 1`` rows).  The previous token of a step's first token is
+    the embedding's own state: two places per slot, indexed by position parity."""
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, vocab_size: int, hidden_size: int, dtype: torch.dtype, device):
+        self.name, self.pair_name, self.norm_name = spec["name"], spec["pair_name"], spec["norm_name"]
+        self.vocab, self.hidden = int(vocab_size), int(hidden_size)
+        self.scale, self.eps = float(spec["scale"]), float(spec["eps"])
+        self.buckets = int(spec["buckets"])
+        self.mul_prev, self.mul_cur = int(spec["mul_prev"]), int(spec["mul_cur"])
+        if self.buckets <= 0:
+            raise ConfigError("pair_embedding: buckets must be positive")
+        self.table: Optional[torch.Tensor] = None
+        self.pairs = self.norm_w = None
+
+    @classmethod
+    def expected(cls, spec: PartSpec, vocab_size: int, hidden_size: int) -> dict:
+        return {spec["name"]: Expected((int(vocab_size), int(hidden_size))),
+                spec["pair_name"]: Expected((int(spec["buckets"]) + 1, int(hidden_size))),
+                spec["norm_name"]: Expected((int(hidden_size),), init="scale")}
+
+    def bind(self, tensors: dict) -> None:
+        self.table = tensors[self.name].contiguous()
+        self.pairs = tensors[self.pair_name].to(self.table.dtype).contiguous()
+        self.norm_w = tensors[self.norm_name].to(torch.float32).contiguous()
+
+    def weights(self):
+        return (self.table, self.pairs, self.norm_w)
+
+    def cache_need(self):
+        from ..cache.storage import StateNeed
+        return StateNeed((2,), torch.int32, by_position=True)
+
+    def forward(self, tok_ids: torch.Tensor, out32: torch.Tensor, ctx, view) -> None:
+        kernels.embed_pair_norm(self.table, self.pairs, tok_ids, ctx, view.states, self.norm_w, self.eps,
+                                self.scale, self.buckets, self.mul_prev, self.mul_cur, out32)
+
+
 register_embedding("token_embedding", TokenEmbedding)
+register_embedding("pair_embedding", PairEmbedding)
 register_head("lm_head", LMHead)
