@@ -262,6 +262,8 @@ def latent_keep(d, norm_w, eps, pages, h, ring, taps, ctx) -> None:
     f = _fn("stream_ops.cu", "g2b_latent_keep",
             [c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p,
              c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    if d is None and ring is None:
+        return
     ref = d if d is not None else h
     if d is not None:
         _need(norm_w, torch.float32, "latent norm weight")
@@ -270,8 +272,8 @@ def latent_keep(d, norm_w, eps, pages, h, ring, taps, ctx) -> None:
     if ring is not None and (ring.dtype != h.dtype or not h.is_contiguous()):
         raise KernelError("latent_keep: ring and rows must have one dtype")
     _call(f, _ptr(d), d.stride(0) if d is not None else 0, d.shape[1] if d is not None else 0,
-          _ptr(norm_w), float(eps), _ptr(pages), _ptr(ctx.page_table), ctx.page_table.shape[1],
-          ctx.page_size, _ptr(h) if ring is not None else None, _ptr(ring),
+          _ptr(norm_w), float(eps), _ptr(pages), _ptr(ctx.page_table) if d is not None else None,
+          ctx.page_table.shape[1] if d is not None else 0, ctx.page_size, _ptr(h) if ring is not None else None, _ptr(ring),
           h.shape[1] if ring is not None else 0, int(taps), _code(ref.dtype), _ptr(ctx.tok_pos),
           _ptr(ctx.tok_seq), _ptr(ctx.seq_slots), ref.shape[0], _stream())
 

@@ -133,6 +133,12 @@ class GatedPreNormBlock:
             out.update(feed_forward_class(layer.feed_forward).expected(layer.feed_forward, H))
             out[names["ffn_gate"]] = Expected((H, H))
             out[names["ffn_gate_bias"]] = Expected((H,))
+        else:
+            # a checkpoint may carry the second sublayer's norm and gate all the same; they are unused
+            out.update({k: Expected(e.shape, e.init, optional=True) for k, e in
+                        norm_class(layer.norm).expected(layer.norm, H, names["ffn_norm"]).items()})
+            out[names["ffn_gate"]] = Expected((H, H), optional=True)
+            out[names["ffn_gate_bias"]] = Expected((H,), optional=True)
         return out
 
     def bind(self, tensors: dict) -> None:
