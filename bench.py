@@ -2,7 +2,7 @@
 """Decode and prefill throughput of gguf2bin_b200 on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode|ragged8|b64] [--batch B] [--layers L] [--context C]
+                    [--workload decode|ragged8|b64|senotar] [--batch B] [--layers L] [--context C]
                     [--no-points] [--sizes 0.6b|8b|14b]
 
 The default run has the layer sizes of Qwen3-0.6B (28 layers, width 1024, 16/8 heads of
@@ -34,6 +34,13 @@ prompts with lengths drawn uniformly from [128, 2048] (seeded) in ONE ragged pro
 tokens per second go under ``prefill``, then 256 decode steps.  ``--workload b64`` runs that of
 the Qwen3-14B configuration (all 40 layers): 64 prompts of 512 tokens in one prompt step, then
 decoding to a context of 2,048.  The weights are made in device memory (no folder is written).
+
+``--workload senotar`` is a comparison, not the benchmark: at three layer sizes it builds a
+Senotar model (latent attention, gated residuals, xIELU feed-forward) and a Qwen3 model with the
+same width, layer count, vocabulary and (within 3 %) parameter count, and times for each one
+prompt step of 2,048 tokens and decode steps at batch 8 behind 2,048-token prompts, on the
+device, with the fraction of the tensor-core peak (prompt) and of the copy bandwidth (decode)
+that each reaches.  It prints one JSON line of its own shape.
 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the
 fallback figures 6.65 TB/s and 1.59 PFLOP/s.  Inputs are synthetic.  Between timed steps
@@ -240,11 +247,98 @@ def hbm_roofline(sizes: dict, batch: int, mean_ctx: float, sec_per_step: float, 
                 frac=achieved / pk["hbm_gbs"], peaks=pk["source"])
 
 
+# ---- Senotar beside Qwen3 at equal sizes --------------------------------------------------------
+# name: (width, heads, qk/v size per head, latent rank, Senotar's ff; Qwen3's kv heads, head size, ff)
+EQUAL_SIZES = {
+    "w1024": (1024, 16, 64, 128, 5632, 8, 128, 3072),
+    "w2048": (2048, 16, 128, 128, 8192, 8, 128, 6144),
+    "w4096": (4096, 32, 128, 128, 15360, 8, 128, 12288),
+}
+
+
+def senotar_config(width, heads, dim, rank, ff, layers, vocab) -> dict:
+    """Every second layer attends over the latents of the layer in front of it."""
+    out = []
+    for i in range(layers):
+        mixer = dict(heads=heads, dim=dim, vdim=dim, kv_rank=rank, scale=dim ** -0.5)
+        if i % 2:
+            mixer["kv_from"] = i - 1
+        out.append(dict(type="latent_attention", mixer=mixer, mlp=dict(kind="dense", ff=ff)))
+    return dict(architecture="Senotar", width=width, vocab=vocab, norm=dict(eps=1e-6), canon=dict(taps=3),
+                embedding=dict(scale=float(width) ** 0.5, bigram=dict(buckets=100003, mul_prev=127, mul_cur=7)),
+                layers=out)
+
+
+def senotar_bytes_and_flops(cfg: dict) -> dict:
+    W, V = cfg["width"], cfg["vocab"]
+    params, cache_bytes_per_token, attn = 0, 0, 0
+    for layer in cfg["layers"]:
+        m, ff = layer["mixer"], layer["mlp"]["ff"]
+        H, dk, dv, r = m["heads"], m["dim"], m["vdim"], m["kv_rank"]
+        params += W * (H * dk + H) + H * dk * r + H * dv * r + W * H * dv + 2 * W * W + 2 * W * ff
+        if "kv_from" not in m:
+            params += r * W
+        cache_bytes_per_token += 2 * r              # every layer's attention reads the latents it attends over
+        attn += 4 * H * r                           # flops per (query, key) pair: scores and sums, both of rank r
+    return dict(layer_params=params, weight_bytes=2 * (params + V * W), kv_bytes_per_token=cache_bytes_per_token,
+                attn_flops_per_pair=attn)
+
+
+def senotar_comparison(a, pk) -> int:
+    import torch
+    from gguf2bin_b200.api import LLM
+    layers, vocab, batch, T = a.layers or 8, 151936, a.batch or 8, a.prefill_tokens
+    steps, warmup = a.steps or 128, max(a.warmup, 8)
+    max_tokens = batch * (T + warmup + steps + 128)
+    rows = {}
+    clocks = ClockSampler()
+    clocks.start()
+    for name, (width, heads, dim, rank, ff, q_kv, q_hd, q_ff) in EQUAL_SIZES.items():
+        if a.sizes_only and name not in a.sizes_only.split(","):
+            continue
+        row = {}
+        for arch in ("senotar", "qwen3"):
+            if arch == "senotar":
+                cfg = senotar_config(width, heads, dim, rank, ff, layers, vocab)
+                sizes = senotar_bytes_and_flops(cfg)
+                flops = 2.0 * T * sizes["layer_params"] + sizes["attn_flops_per_pair"] * T * (T + 1) / 2 + 2.0 * vocab * width
+            else:
+                cfg = dict(QWEN3_0P6B, hidden_size=width, intermediate_size=q_ff, num_hidden_layers=layers,
+                           num_attention_heads=heads, num_key_value_heads=q_kv, head_dim=q_hd, vocab_size=vocab,
+                           tie_word_embeddings=False)
+                sizes = model_bytes_and_flops(cfg, layers)
+                sizes["layer_params"] *= layers
+                flops = prefill_flops(cfg, layers, [T])
+            llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seqs=batch + 1)
+            first, ms, plain = timed_prompt_step(llm, random_prompts(1, T, vocab, 1), repeats=3)
+            sec, per_step, mean_ctx = decode_device_timed(llm, random_prompts(batch, T, vocab, 100), steps, warmup,
+                                                          vocab, whole_batch_prefill=False)
+            roof = hbm_roofline(sizes, batch, mean_ctx, sec / steps, pk)
+            row[arch] = dict(
+                parameters_per_layer_m=round(sizes["layer_params"] / layers / 1e6, 1),
+                prefill_tokens_per_s=round(T / (ms / 1e3)), prefill_ms=round(ms, 3), prefill_plain_ms=round(plain, 3),
+                prefill_frac_of_tensor_peak=round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+                decode_tokens_per_s=round(batch * steps / sec), decode_ms_per_step=round(sec / steps * 1e3, 4),
+                decode_launches_per_step=per_step, decode_gbs=round(roof["achieved"]),
+                decode_frac_of_copy_bandwidth=round(roof["frac"], 3))
+            del llm
+            torch.cuda.empty_cache()
+        rows[name] = row
+    print(json.dumps({"metric": "prefill and decode tokens/s of Senotar beside Qwen3 at equal sizes (random weights)",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+                      "config": {"layers": layers, "vocab": vocab, "prompt_tokens": T, "decode_batch": batch,
+                                 "decode_context_from": T + warmup, "decode_steps": steps, "peaks": pk["source"],
+                                 "l2": "inputs larger than L2 (weights + cache read every step)"},
+                      "sizes": rows, "clocks": clocks.stop()}))
+    return 0
+
+
 WORKLOADS = {
     # name: (sizes, batch, what it is)
     "decode": ("0.6b", 8, "every sequence prefilled to half the context, then decoded"),
     "ragged8": ("8b", 8, "8 prompts with lengths uniform in [128, 2048] in ONE prompt step, then 256 decode steps"),
     "b64": ("14b", 64, "64 prompts of 512 tokens in one prompt step, decoded to a context of 2048"),
+    "senotar": (None, 8, "Senotar beside Qwen3 at equal sizes: a 2,048-token prompt step and batch-8 decode steps each"),
 }
 
 
@@ -264,6 +358,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the prompt of the prefill figure (decode workload; default 2048)")
+    ap.add_argument("--sizes-only", default=None,
+                    help="senotar workload: a comma-separated subset of " + ",".join(EQUAL_SIZES))
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -277,6 +373,8 @@ def main() -> int:
         return 2
     if a.warmup < 3:
         a.warmup = 3
+    if a.workload == "senotar":
+        return senotar_comparison(a, peaks())
 
     import numpy as np
     import torch

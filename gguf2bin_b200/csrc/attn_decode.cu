@@ -240,7 +240,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
                    const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
                    const int *__restrict__ page_table, int P, int nh, int nkv, int window,
                    float scale_log2, float *__restrict__ part_o, float2 *__restrict__ part_ml,
-                   int n_chunks) {
+                   int n_chunks, int planes) {
   pdl_launch();
   extern __shared__ __align__(128) unsigned char smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -260,7 +260,8 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
   const int b = tok_seq[t];
   auto panel_of = [&](int pg, int kv) {
     const int phys = page_table[(size_t)b * P + pg];
-    return cache + (((size_t)phys * 2 + kv) * nkv + kvh) * panel_elems;
+    // planes == 1: the page's one panel per kv head is read as keys and again as values
+    return cache + (((size_t)phys * planes + kv * (planes - 1)) * nkv + kvh) * panel_elems;
   };
 
   // Before the kernels in front of this one are done (they compute this token's query and
@@ -334,7 +335,7 @@ constexpr int COMBINE_WARPS = 4;
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
                     const int *__restrict__ tok_pos, int nh, int window, int n_chunks,
-                    bf16 *__restrict__ out) {
+                    bf16 *__restrict__ out, const float *__restrict__ sink) {
   pdl_launch();
   pdl_wait();
   __shared__ float s_max[COMBINE_WARPS];
@@ -389,7 +390,8 @@ attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__
   __syncthreads();
   for (int d = threadIdx.x; d < HD; d += COMBINE_WARPS * 32) {
     const float n = ((s_acc[0][d] + s_acc[1][d]) + s_acc[2][d]) + s_acc[3][d];
-    const float dn = ((s_acc[0][HD] + s_acc[1][HD]) + s_acc[2][HD]) + s_acc[3][HD];
+    float dn = ((s_acc[0][HD] + s_acc[1][HD]) + s_acc[2][HD]) + s_acc[3][HD];
+    if (sink) dn += exp2f(sink[th % nh] * LOG2E - M);          // a term without key or value, not scaled
     out[th * HD + d] = __float2bfloat16_rn(n / dn);
   }
 }
@@ -405,8 +407,9 @@ extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, cons
                                const int *tok_seq, const int *page_table, int P, int T, int nh,
                                int nkv, int hd, int page_size, int window, float scale,
                                int max_kv_len, float *part_o, float *part_ml,
-                               cudaStream_t stream) {
+                               const float *sink, int planes, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (planes != 1 && planes != 2) G2B_REFUSE("attn_decode: %d panels per page and kv head (1 or 2)", planes);
   if (hd != HD) G2B_REFUSE("attn_decode: built for head_dim %d, got %d", HD, hd);
   if (page_size != PAGE) G2B_REFUSE("attn_decode: page size must be %d, got %d", PAGE, page_size);
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_decode: %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -427,11 +430,11 @@ extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, cons
   dim3 grid(n_chunks, nkv * head_tiles, T);
   g2b_launch(attn_decode_kernel, dim3(grid), dim3(WARPS * 32), smem, stream, 
       (const bf16 *)q, (const bf16 *)cache, tok_pos, tok_seq, page_table, P, nh, nkv, window,
-      scale * LOG2E, part_o, (float2 *)part_ml, n_chunks);
+      scale * LOG2E, part_o, (float2 *)part_ml, n_chunks, planes);
   int rc = g2b_check_launch("attn_decode");
   if (rc) return rc;
   g2b_launch(attn_combine_kernel, dim3((unsigned)((size_t)T * nh)), dim3(COMBINE_WARPS * 32), 0, stream, 
-      part_o, (const float2 *)part_ml, tok_pos, nh, window, n_chunks, (bf16 *)out);
+      part_o, (const float2 *)part_ml, tok_pos, nh, window, n_chunks, (bf16 *)out, sink);
   return g2b_check_launch("attn_combine");
 }
 

@@ -122,7 +122,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_kv, bf16 *__restrict__ out,
                        const int4 *__restrict__ tiles, const int *__restrict__ page_table, int P,
                        int nh, int nkv, int window, float scale_log2, int first_wave,
-                       int *__restrict__ status) {
+                       int *__restrict__ status, const float *__restrict__ sink, int planes) {
   pdl_launch();
   // The swizzled panels need 1024-byte alignment.  The kernel has no static shared memory, so
   // the dynamic part starts at the aligned base of the window; checked rather than assumed.
@@ -191,7 +191,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       auto load_k = [&](int i) -> bool {
         const int s = i % K_STAGES;
         if (i >= K_STAGES && !mbar_wait(k_empty0 + 8 * s, ((i / K_STAGES) - 1) & 1)) return false;
-        const int row = ((pt[i] * 2 + 0) * nkv + kvh) * PAGE;
+        const int row = ((pt[i] * planes + 0) * nkv + kvh) * PAGE;
         const uint32_t dst = smem_addr(k_smem + s * KV_BYTES);
         mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
 #pragma unroll
@@ -202,7 +202,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       auto load_v = [&](int i) -> bool {
         const int s = i % V_STAGES;
         if (i >= V_STAGES && !mbar_wait(v_empty0 + 8 * s, ((i / V_STAGES) - 1) & 1)) return false;
-        const int row = ((pt[i] * 2 + 1) * nkv + kvh) * PAGE;
+        const int row = ((pt[i] * planes + (planes - 1)) * nkv + kvh) * PAGE;      // one panel: it is keys and values
         const uint32_t dst = smem_addr(v_smem + s * KV_BYTES);
         mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
 #pragma unroll
@@ -414,6 +414,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
         l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
         l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        if (sink) {                                // one more term in the denominator: no key, no value, not scaled
+          const float s2 = sink[h] * LOG2E;
+          l_a += ex2(s2 - m_a);
+          l_b += ex2(s2 - m_b);
+        }
         const float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
         bf16 *op_a = out + ((size_t)(t0 + rA) * nh + h) * HD + 2 * c;
         bf16 *op_b = out + ((size_t)(t0 + rB) * nh + h) * HD + 2 * c;
@@ -448,21 +453,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, long long n_cache_pages,
                                    const int *tiles, int n_tiles, const int *page_table, int P,
                                    int T, int nh, int nkv, int hd, int page_size, int window,
-                                   float scale, int *status, cudaStream_t stream) {
+                                   float scale, const float *sink, int planes, int *status,
+                                   cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (hd != HD) G2B_REFUSE("attn_prefill_tc: built for head_dim %d, got %d", HD, hd);
   if (page_size != PAGE) G2B_REFUSE("attn_prefill_tc: page size must be %d, got %d", PAGE, page_size);
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_prefill_tc: %d heads are not a multiple of %d kv heads", nh, nkv);
   if ((long long)n_tiles * nh > 0x7fffffffLL) G2B_REFUSE("attn_prefill_tc: %d tiles x %d heads", n_tiles, nh);
   if (!status) G2B_REFUSE("attn_prefill_tc: no status word");
+  if (planes != 1 && planes != 2) G2B_REFUSE("attn_prefill_tc: %d panels per page and kv head (1 or 2)", planes);
   if (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15)
     G2B_REFUSE("attn_prefill_tc: q, out and the cache must be 16-byte aligned");
-  if (n_cache_pages * 2 * nkv * PAGE > 0x7fffffffLL)
+  if (n_cache_pages * planes * nkv * PAGE > 0x7fffffffLL)
     G2B_REFUSE("attn_prefill_tc: the cache layer has too many rows for 32-bit copy coordinates");
   CUtensorMap mq, mkv;
   int rc = get_map(&mq, q, T, nh * HD, nh * HD, BM);
   if (rc) G2B_REFUSE("attn_prefill_tc: tensor map of q failed (%d)", rc);
-  rc = get_map(&mkv, cache, n_cache_pages * 2 * nkv * PAGE, HD, HD, PAGE);
+  rc = get_map(&mkv, cache, n_cache_pages * planes * nkv * PAGE, HD, HD, PAGE);
   if (rc) G2B_REFUSE("attn_prefill_tc: tensor map of the cache failed (%d)", rc);
   static G2bPerDevice configured;                      // holds the device's SM count once it is set up
   const int cfg_dev = g2b_current_device();
@@ -478,7 +485,7 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
     if (cfg_dev >= 0) configured.value[cfg_dev] = n_sms;
   }
   g2b_launch(attn_prefill_tc_kernel, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
-             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status);
+             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status, sink, planes);
   return g2b_check_launch("attn_prefill_tc");
 }
 

@@ -105,37 +105,91 @@ extern "C" int g2b_embed_pair_norm(const void *table, const void *pairs, int tab
 }
 
 // ---------------------------------------------------------------------------
-// causal convolution over time on each channel, added to its input
+// causal convolution over time on each channel, added to its input.  One block per token; a
+// thread takes eight neighbouring channels (16-byte loads) when the width allows, else one.
 // ---------------------------------------------------------------------------
 #define CANON_MAX_TAPS 16
 
-template <typename TA>
+template <typename TA> struct Vec8;
+template <> struct Vec8<bf16> {
+  uint4 raw;
+  __device__ __forceinline__ void load(const bf16 *p) { raw = *reinterpret_cast<const uint4 *>(p); }
+  __device__ __forceinline__ void store(bf16 *p) const { *reinterpret_cast<uint4 *>(p) = raw; }
+  __device__ __forceinline__ float get(int i) const {
+    const uint32_t w = (&raw.x)[i >> 1];
+    return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
+  }
+  __device__ __forceinline__ void set(const float (&v)[8]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      (&raw.x)[i] = *reinterpret_cast<uint32_t *>(&p2);
+    }
+  }
+};
+template <> struct Vec8<float> {
+  float4 lo, hi;
+  __device__ __forceinline__ void load(const float *p) {
+    lo = *reinterpret_cast<const float4 *>(p);
+    hi = *reinterpret_cast<const float4 *>(p + 4);
+  }
+  __device__ __forceinline__ void store(float *p) const {
+    *reinterpret_cast<float4 *>(p) = lo;
+    *reinterpret_cast<float4 *>(p + 4) = hi;
+  }
+  __device__ __forceinline__ float get(int i) const { return i < 4 ? (&lo.x)[i] : (&hi.x)[i - 4]; }
+  __device__ __forceinline__ void set(const float (&v)[8]) {
+    lo = make_float4(v[0], v[1], v[2], v[3]);
+    hi = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+
+template <typename TA, bool VEC>
 __global__ void __launch_bounds__(256)
 canon_conv_kernel(const TA *__restrict__ h, const float *__restrict__ w, const TA *__restrict__ ring,
                   const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
                   const int *__restrict__ seq_slots, TA *__restrict__ out, int T, int H, int taps) {
   pdl_launch();
   pdl_wait();
-  const int t = blockIdx.y;
-  const int b = tok_seq[t], pos = tok_pos[t];
-  const TA *src[CANON_MAX_TAPS];                      // row that lies k steps back; nullptr: before the start
-  const TA *my_ring = ring + (size_t)seq_slots[b] * taps * H;
+  __shared__ const TA *src[CANON_MAX_TAPS];           // the row that lies k steps back; nullptr: before the start
+  const int t = blockIdx.x;
+  if (threadIdx.x < taps) {
+    const int k = threadIdx.x, b = tok_seq[t], pos = tok_pos[t];
+    const TA *p = nullptr;
+    if (pos - k >= 0) {
+      if (t - k >= 0 && tok_seq[t - k] == b) p = h + (size_t)(t - k) * H;
+      else p = ring + ((size_t)seq_slots[b] * taps + (pos - k) % taps) * H;
+    }
+    src[k] = p;
+  }
+  __syncthreads();
+  if (VEC) {
+    for (int j = 8 * threadIdx.x; j < H; j += 8 * blockDim.x) {
+      float acc[8];
 #pragma unroll
-  for (int k = 0; k < CANON_MAX_TAPS; ++k) {
-    src[k] = nullptr;
-    if (k < taps && pos - k >= 0) {
-      if (t - k >= 0 && tok_seq[t - k] == b) src[k] = h + (size_t)(t - k) * H;
-      else src[k] = my_ring + (size_t)((pos - k) % taps) * H;
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int k = taps - 1; k >= 0; --k) {            // oldest first: the order of the taps
+        if (!src[k]) continue;
+        Vec8<TA> v;
+        v.load(src[k] + j);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[(size_t)(j + i) * taps + (taps - 1 - k)], v.get(i), acc[i]);
+      }
+      Vec8<TA> own;
+      own.load(src[0] + j);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += own.get(i);
+      own.set(acc);
+      own.store(out + (size_t)t * H + j);
+    }
+  } else {
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+      float acc = 0.f;
+      for (int k = taps - 1; k >= 0; --k)
+        if (src[k]) acc = fmaf(w[(size_t)j * taps + (taps - 1 - k)], to_f32(src[k][j]), acc);
+      out[(size_t)t * H + j] = from_f32<TA>(to_f32(src[0][j]) + acc);
     }
   }
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= H) return;
-  const float own = to_f32(src[0][j]);
-  float acc = 0.f;
-#pragma unroll
-  for (int k = CANON_MAX_TAPS - 1; k >= 0; --k)        // oldest first: the order of the taps
-    if (k < taps && src[k]) acc = fmaf(w[(size_t)j * taps + (taps - 1 - k)], to_f32(src[k][j]), acc);
-  out[(size_t)t * H + j] = from_f32<TA>(own + acc);
 }
 
 extern "C" int g2b_canon_conv(const void *h, const float *w, const void *ring, int dtype,
@@ -143,16 +197,21 @@ extern "C" int g2b_canon_conv(const void *h, const float *w, const void *ring, i
                               void *out, int T, int H, int taps, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (taps < 1 || taps > CANON_MAX_TAPS) G2B_REFUSE("canon_conv: %d taps outside 1..%d", taps, CANON_MAX_TAPS);
-  const int threads = H >= 256 ? 256 : 64;
-  const dim3 grid((H + threads - 1) / threads, T);
-  if (dtype == G2B_F32)
-    g2b_launch(canon_conv_kernel<float>, grid, dim3(threads), 0, stream, (const float *)h, w,
-               (const float *)ring, tok_pos, tok_seq, seq_slots, (float *)out, T, H, taps);
-  else if (dtype == G2B_BF16)
-    g2b_launch(canon_conv_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16 *)h, w,
-               (const bf16 *)ring, tok_pos, tok_seq, seq_slots, (bf16 *)out, T, H, taps);
-  else
+  const bool vec = H % 8 == 0 && (((uintptr_t)h | (uintptr_t)ring | (uintptr_t)out) & 15) == 0;
+  const int per = vec ? 8 : 1;
+  int threads = (H / per + 31) / 32 * 32;
+  threads = threads < 32 ? 32 : (threads > 256 ? 256 : threads);
+  if (dtype == G2B_F32) {
+    auto k = vec ? canon_conv_kernel<float, true> : canon_conv_kernel<float, false>;
+    g2b_launch(k, dim3(T), dim3(threads), 0, stream, (const float *)h, w, (const float *)ring, tok_pos,
+               tok_seq, seq_slots, (float *)out, T, H, taps);
+  } else if (dtype == G2B_BF16) {
+    auto k = vec ? canon_conv_kernel<bf16, true> : canon_conv_kernel<bf16, false>;
+    g2b_launch(k, dim3(T), dim3(threads), 0, stream, (const bf16 *)h, w, (const bf16 *)ring, tok_pos,
+               tok_seq, seq_slots, (bf16 *)out, T, H, taps);
+  } else {
     G2B_REFUSE("canon_conv: unknown dtype %d", dtype);
+  }
   return g2b_check_launch("canon_conv");
 }
 
@@ -226,6 +285,7 @@ extern "C" int g2b_latent_keep(const void *d, int d_stride, int rank, const floa
 // ---------------------------------------------------------------------------
 #define HP_ROWS 8
 #define HP_THREADS 256
+#define HP_COLS 64            // absorb: output columns per block (two per lane), the inner index dealt to the 8 warps
 
 template <typename TA>
 __global__ void __launch_bounds__(HP_THREADS)
@@ -233,30 +293,48 @@ head_absorb_kernel(const TA *__restrict__ in, int in_stride, const TA *__restric
                    TA *__restrict__ out, int out_stride, int T, int heads, int n, int r) {
   pdl_launch();
   pdl_wait();
-  extern __shared__ float hp_smem[];                  // [HP_ROWS][n]
-  const int h = blockIdx.x, t0 = blockIdx.y * HP_ROWS;
+  extern __shared__ float hp_smem[];                  // [HP_ROWS][n], then [8 warps][HP_ROWS][HP_COLS]
+  float *part = hp_smem + HP_ROWS * n;
+  const int h = blockIdx.x, t0 = blockIdx.y * HP_ROWS, c0 = blockIdx.z * HP_COLS;
   const int rows = min(HP_ROWS, T - t0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < HP_ROWS * n; i += blockDim.x) {
     const int m = i / n, k = i % n;
     hp_smem[i] = m < rows ? to_f32(in[(size_t)(t0 + m) * in_stride + (size_t)h * n + k]) : 0.f;
   }
   __syncthreads();
   const TA *Wh = W + (size_t)h * n * r;
-  for (int c = threadIdx.x; c < r; c += blockDim.x) {
-    float acc[HP_ROWS];
+  const int ca = c0 + 2 * lane, cb = ca + 1;
+  float acc[HP_ROWS][2];
 #pragma unroll
-    for (int m = 0; m < HP_ROWS; ++m) acc[m] = 0.f;
-    for (int k = 0; k < n; ++k) {
-      const float w = to_f32(Wh[(size_t)k * r + c]);
+  for (int m = 0; m < HP_ROWS; ++m) acc[m][0] = acc[m][1] = 0.f;
+  for (int k = warp; k < n; k += HP_THREADS / 32) {    // warp w: inner indices w, w + 8, ...
+    const float wa = ca < r ? to_f32(Wh[(size_t)k * r + ca]) : 0.f;
+    const float wb = cb < r ? to_f32(Wh[(size_t)k * r + cb]) : 0.f;
 #pragma unroll
-      for (int m = 0; m < HP_ROWS; ++m) acc[m] = fmaf(w, hp_smem[m * n + k], acc[m]);
+    for (int m = 0; m < HP_ROWS; ++m) {
+      const float x = hp_smem[m * n + k];
+      acc[m][0] = fmaf(wa, x, acc[m][0]);
+      acc[m][1] = fmaf(wb, x, acc[m][1]);
     }
+  }
 #pragma unroll
-    for (int m = 0; m < HP_ROWS; ++m)
-      if (m < rows) out[(size_t)(t0 + m) * out_stride + (size_t)h * r + c] = from_f32<TA>(acc[m]);
+  for (int m = 0; m < HP_ROWS; ++m) {
+    part[(warp * HP_ROWS + m) * HP_COLS + 2 * lane] = acc[m][0];
+    part[(warp * HP_ROWS + m) * HP_COLS + 2 * lane + 1] = acc[m][1];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < HP_ROWS * HP_COLS; i += blockDim.x) {     // the warps' parts in warp order
+    const int m = i / HP_COLS, c = i % HP_COLS;
+    if (m >= rows || c0 + c >= r) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < HP_THREADS / 32; ++wi) v += part[(wi * HP_ROWS + m) * HP_COLS + c];
+    out[(size_t)(t0 + m) * out_stride + (size_t)h * r + c0 + c] = from_f32<TA>(v);
   }
 }
 
+// expand: a warp per output number of a head (8 per block), lanes over the rank
 template <typename TA>
 __global__ void __launch_bounds__(HP_THREADS)
 head_expand_kernel(const TA *__restrict__ in, int in_stride, const TA *__restrict__ W,
@@ -272,28 +350,26 @@ head_expand_kernel(const TA *__restrict__ in, int in_stride, const TA *__restric
     hp_smem[i] = m < rows ? to_f32(in[(size_t)(t0 + m) * in_stride + (size_t)h * r + k]) : 0.f;
   }
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-  for (int i = warp; i < n; i += n_warps) {
-    const TA *wr = W + ((size_t)h * n + i) * r;
-    float acc[HP_ROWS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i = blockIdx.z * (HP_THREADS / 32) + warp;
+  if (i >= n) return;
+  const TA *wr = W + ((size_t)h * n + i) * r;
+  float acc[HP_ROWS];
 #pragma unroll
-    for (int m = 0; m < HP_ROWS; ++m) acc[m] = 0.f;
-    for (int k = lane; k < r; k += 32) {
-      const float w = to_f32(wr[k]);
+  for (int m = 0; m < HP_ROWS; ++m) acc[m] = 0.f;
+  for (int k = lane; k < r; k += 32) {
+    const float w = to_f32(wr[k]);
 #pragma unroll
-      for (int m = 0; m < HP_ROWS; ++m) acc[m] = fmaf(w, hp_smem[m * r + k], acc[m]);
-    }
+    for (int m = 0; m < HP_ROWS; ++m) acc[m] = fmaf(w, hp_smem[m * r + k], acc[m]);
+  }
 #pragma unroll
-    for (int m = 0; m < HP_ROWS; ++m) acc[m] = warp_sum(acc[m]);
-    if (lane == 0) {
+  for (int m = 0; m < HP_ROWS; ++m) acc[m] = warp_sum(acc[m]);
+  if (lane < rows) {
+    float v = acc[0];
 #pragma unroll
-      for (int m = 0; m < HP_ROWS; ++m)
-        if (m < rows) {
-          float v = acc[m];
-          if (gate) v *= sigmoid_f(to_f32(gate[(size_t)(t0 + m) * gate_stride + h]));
-          out[(size_t)(t0 + m) * out_stride + (size_t)h * n + i] = from_f32<TA>(v);
-        }
-    }
+    for (int m = 1; m < HP_ROWS; ++m) v = lane == m ? acc[m] : v;
+    if (gate) v *= sigmoid_f(to_f32(gate[(size_t)(t0 + lane) * gate_stride + h]));
+    out[(size_t)(t0 + lane) * out_stride + (size_t)h * n + i] = from_f32<TA>(v);
   }
 }
 
@@ -302,9 +378,11 @@ extern "C" int g2b_head_product(const void *in, int in_stride, const void *W, co
                                 int r, int expand, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (heads <= 0 || n <= 0 || r <= 0) G2B_REFUSE("head_product: bad sizes heads=%d n=%d r=%d", heads, n, r);
-  const size_t smem = sizeof(float) * HP_ROWS * (size_t)(expand ? r : n);
+  const size_t smem = sizeof(float) * HP_ROWS * (size_t)(expand ? r : n + (HP_THREADS / 32) * HP_COLS);
   if (smem > 48 * 1024) G2B_REFUSE("head_product: %d values per head and token are more than fit", expand ? r : n);
-  const dim3 grid(heads, (T + HP_ROWS - 1) / HP_ROWS);
+  const dim3 grid(heads, (T + HP_ROWS - 1) / HP_ROWS,
+                  expand ? (n + HP_THREADS / 32 - 1) / (HP_THREADS / 32) : (r + HP_COLS - 1) / HP_COLS);
+  if (grid.y > 65535 || grid.z > 65535) G2B_REFUSE("head_product: %d tokens or %d outputs per head are too many", T, expand ? n : r);
   if (dtype == G2B_F32) {
     if (expand)
       g2b_launch(head_expand_kernel<float>, grid, dim3(HP_THREADS), smem, stream, (const float *)in, in_stride,
@@ -359,7 +437,7 @@ extern "C" int g2b_head_gate(void *o, const void *gate, int gate_stride, int T, 
 // (the norm in front of the next sublayer).  One block per row.
 // ---------------------------------------------------------------------------
 template <typename TA>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 gated_add_kernel(float *__restrict__ x, const float *__restrict__ y, const TA *__restrict__ g,
                  int g_stride, const float *__restrict__ bias, int H, const float *__restrict__ norm_w,
                  float eps, TA *__restrict__ normed) {
@@ -389,7 +467,8 @@ extern "C" int g2b_gated_add(float *x, const float *y, const void *g, int g_stri
                              int T, int H, const float *norm_w, float eps, void *normed, int dtype,
                              cudaStream_t stream) {
   if (T <= 0) return 0;
-  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  int threads = (H / 2 + 31) / 32 * 32;                // two elements a thread, up to 1,024 threads
+  threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
   if (dtype == G2B_F32)
     g2b_launch(gated_add_kernel<float>, dim3(T), dim3(threads), 0, stream, x, y, (const float *)g, g_stride,
                bias, H, norm_w, eps, (float *)normed);
@@ -404,31 +483,53 @@ extern "C" int g2b_gated_add(float *x, const float *y, const void *g, int g_stri
 // ---------------------------------------------------------------------------
 // xIELU on the first F columns of a [T, stride] buffer
 // ---------------------------------------------------------------------------
-template <typename TA>
-__global__ void xielu_kernel(const TA *__restrict__ in, int in_stride, const float *__restrict__ pq,
-                             TA *__restrict__ out, int F, long long total) {
+template <typename TA, bool VEC>
+__global__ void __launch_bounds__(256)
+xielu_kernel(const TA *__restrict__ in, int in_stride, const float *__restrict__ pq,
+             TA *__restrict__ out, int F) {
   pdl_launch();
   pdl_wait();
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
   const float a = softplus_f(pq[0]), bq = 0.5f + softplus_f(pq[1]);
-  const float z = to_f32(in[(i / F) * in_stride + i % F]);
-  const float v = z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(bq, expm1f(z) - z, 0.5f * z);
-  out[i] = from_f32<TA>(v);
+  const TA *row = in + (size_t)blockIdx.x * in_stride;           // rows along x: a step may have any number of them
+  TA *orow = out + (size_t)blockIdx.x * F;
+  if (VEC) {
+    const int j = 8 * (blockIdx.y * blockDim.x + threadIdx.x);
+    if (j >= F) return;
+    Vec8<TA> v;
+    v.load(row + j);
+    float r[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float z = v.get(i);
+      r[i] = z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(bq, expm1f(z) - z, 0.5f * z);
+    }
+    v.set(r);
+    v.store(orow + j);
+  } else {
+    const int j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j >= F) return;
+    const float z = to_f32(row[j]);
+    orow[j] = from_f32<TA>(z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(bq, expm1f(z) - z, 0.5f * z));
+  }
 }
 
 extern "C" int g2b_xielu(const void *in, int in_stride, const float *pq, void *out, int T, int F,
                          int dtype, cudaStream_t stream) {
-  const long long total = (long long)T * F;
-  if (total <= 0) return 0;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (dtype == G2B_F32)
-    g2b_launch(xielu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *)in, in_stride, pq,
-               (float *)out, F, total);
-  else if (dtype == G2B_BF16)
-    g2b_launch(xielu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16 *)in, in_stride, pq,
-               (bf16 *)out, F, total);
-  else
+  if (T <= 0 || F <= 0) return 0;
+  const size_t es = dtype == G2B_F32 ? 4 : 2;
+  const bool vec = F % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                   ((size_t)in_stride * es) % 16 == 0;
+  const int per = vec ? 8 : 1;
+  const dim3 grid(T, ((F + per - 1) / per + 255) / 256);
+  if (grid.y > 65535) G2B_REFUSE("xielu: %d columns are too many", F);
+  if (dtype == G2B_F32) {
+    auto k = vec ? xielu_kernel<float, true> : xielu_kernel<float, false>;
+    g2b_launch(k, grid, dim3(256), 0, stream, (const float *)in, in_stride, pq, (float *)out, F);
+  } else if (dtype == G2B_BF16) {
+    auto k = vec ? xielu_kernel<bf16, true> : xielu_kernel<bf16, false>;
+    g2b_launch(k, grid, dim3(256), 0, stream, (const bf16 *)in, in_stride, pq, (bf16 *)out, F);
+  } else {
     G2B_REFUSE("xielu: unknown dtype %d", dtype);
+  }
   return g2b_check_launch("xielu");
 }

@@ -5,6 +5,10 @@ bandwidth or FLOP/s.
 
     python -m gguf2bin_b200.kernel_bench decode  [--batch 8] [--ctx 3072] [--only NAME] [--layers 28]
     python -m gguf2bin_b200.kernel_bench prefill [--tokens 2048] [--only NAME] [--layers 4]
+    python -m gguf2bin_b200.kernel_bench latent-decode | latent-prefill  [--rank 128] ...
+
+The ``latent-*`` modes time the kernels of a gated layer with latent attention (``--heads`` heads of
+``--head-dim`` key and value numbers, ``--rank`` cached numbers per token) at the same geometry.
 
 Sizes default to Qwen3-0.6B (width 1024, 16/8 heads of 128, feed-forward 3072, vocabulary
 151936); --hidden/--inter/--heads/--kv-heads/--vocab change them.  Decode kernels run
@@ -205,9 +209,99 @@ def prefill(a) -> None:
     kernels_bf16.check_status()
 
 
+def latent(a, single: bool) -> None:
+    """The kernels of a gated pre-norm layer with latent attention: ``single``: a decode step of
+    ``--batch`` sequences behind ``--ctx`` tokens; else one prompt of ``--tokens`` tokens."""
+    L, H, I, nh, dk, r = a.layers, a.hidden, a.inter, a.heads, a.head_dim, a.rank
+    B = a.batch if single else 1
+    n = 1 if single else a.tokens
+    T = B * n
+    past = a.ctx if single else 0
+    b = Bench(a)
+    ps = 64
+    pages_per = -(-(past + n) // ps)
+    table = torch.arange(B * pages_per, dtype=torch.int32, device=DEV).view(B, pages_per)
+    pos = (torch.arange(n, dtype=torch.int32, device=DEV) + past).repeat(B)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV).repeat_interleave(n)
+    wide = sorted([(s, s * n + r0, min(128, n - r0), past + r0) for s in range(B) for r0 in range(0, n, 128)],
+                  key=lambda t: -(t[3] + t[2]))
+    ctx = SimpleNamespace(tok_pos=pos, tok_seq=seq, page_table=table, page_size=ps, n_tokens=T, n_seqs=B,
+                          seq_slots=torch.arange(B, dtype=torch.int32, device=DEV), seq_meta=None if single else
+                          torch.tensor([[0, n, 0, 0]], dtype=torch.int32, device=DEV),
+                          max_kv_len=pages_per * ps, kv_len_hint=past + n, workspace=Workspace(DEV), all_single=single,
+                          attn_tiles_wide=torch.tensor(wide, dtype=torch.int32, device=DEV), n_attn_tiles_wide=len(wide),
+                          attn_tiles=None, n_attn_tiles=0)
+    n_in = -(-(nh * dk + r + nh) // 8) * 8
+    h, u = bf(T, H), bf(T, H)
+    x32, y32 = torch.randn(T, H, device=DEV), torch.randn(T, H, device=DEV)
+    nw, bias = torch.ones(H, device=DEV), torch.zeros(H, device=DEV)
+    proj = torch.empty(T, n_in, dtype=torch.bfloat16, device=DEV)
+    gate = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    mm = (lambda N, K: dict(nbytes=N * K * 2)) if single else (lambda N, K: dict(flops=2 * T * N * K))
+    hb = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    b.run("rmsnorm", lambda: [kernels.rmsnorm(x32, nw, 1e-6, hb) for _ in range(L)], L, nbytes=T * H * 6)
+    ring = torch.zeros(B + 1, 3, H, dtype=torch.bfloat16, device=DEV)
+    cw = torch.randn(H, 3, device=DEV)
+    b.run("canon_conv", lambda: [kernels.canon_conv(h, cw, ring, ctx, u) for _ in range(L)], L, nbytes=T * H * 4)
+    if b.want("in_proj"):
+        W = [bf(n_in, H) for _ in range(L)]
+        b.run("in_proj", lambda: [kernels_bf16.linear_bf16(u, w, proj, False) for w in W], L, **mm(n_in, H))
+    if b.want("gate_proj"):
+        W = [bf(H, H) for _ in range(L)]
+        b.run("gate_proj", lambda: [kernels_bf16.linear_bf16(h, w, gate, False) for w in W], L, **mm(H, H))
+    caches = [torch.randn(B * pages_per + 1, 1, 1, ps, r, device=DEV).to(torch.bfloat16) for _ in range(L)]
+    cn = torch.ones(r, device=DEV)
+    d = proj[:, nh * dk:nh * dk + r]
+    b.run("latent_keep", lambda: [kernels.latent_keep(d, cn, 1e-6, c, h, ring, 3, ctx) for c in caches], L,
+          nbytes=T * r * 4)
+    uk, uv = [bf(nh * dk, r) for _ in range(L)], [bf(nh * dk, r) for _ in range(L)]
+    qa, mix = bf(T, nh * r), bf(T, nh * r)
+    o = torch.empty(T, nh * dk, dtype=torch.bfloat16, device=DEV)
+    q = proj[:, :nh * dk]
+    g = proj[:, nh * dk + r:nh * dk + r + nh]
+    hp = dict(nbytes=nh * dk * r * 2) if single else dict(flops=2 * T * nh * dk * r)
+    if single:
+        b.run("head_absorb", lambda: [kernels.head_product(q, w, qa, nh, False) for w in uk], L, **hp)
+        b.run("head_expand", lambda: [kernels.head_product(mix, w, o, nh, True, g) for w in uv], L, **hp)
+    else:
+        from .parts.latent import LatentAttention
+        from .config.specs import PartSpec
+        spec = PartSpec.make("latent_attention", n_heads=nh, qk_dim=dk, v_dim=dk, kv_rank=r, scale=dk ** -0.5, eps=1e-6,
+                             names=())
+        m = LatentAttention(spec, H, torch.bfloat16, DEV)
+        m.w_uk, m.w_uv = uk[0], uv[0]
+        b.run("head_absorb", lambda: [m._per_head(q, m.w_uk, qa, False, None) for _ in range(L)], L, **hp)
+        b.run("head_expand", lambda: [m._per_head(mix, m.w_uv, o, True, g) for _ in range(L)], L, **hp)
+    b.run("head_gate", lambda: [kernels.head_gate(mix, g, nh) for _ in range(L)], L, nbytes=T * nh * r * 4)
+    sink = torch.zeros(nh, device=DEV)
+    if single:
+        b.run("attn_latent", lambda: [kernels.attention(qa, mix, c, ctx, nh, 1, r, ps, 0, 0.1, sink=sink, planes=1)
+                                      for c in caches], L, nbytes=B * (past + 1) * r * 2)
+    else:
+        b.run("attn_latent", lambda: [kernels.attention(qa, mix, c, ctx, nh, 1, r, ps, 0, 0.1, sink=sink, planes=1)
+                                      for c in caches], L, flops=4 * nh * r * n * (n + 1) / 2)
+    if b.want("o_proj"):
+        W = [bf(H, nh * dk) for _ in range(L)]
+        b.run("o_proj", lambda: [kernels_bf16.linear_bf16(o, w, y32, False) for w in W], L, **mm(H, nh * dk))
+    b.run("gated_add_norm", lambda: [kernels.gated_add(x32, y32, gate, bias, nw, 1e-6, hb) for _ in range(L)], L,
+          nbytes=T * H * 16)
+    if b.want("up_and_gate"):
+        n_up = I + H
+        W = [bf(n_up, H) for _ in range(L)]
+        up = torch.empty(T, n_up, dtype=torch.bfloat16, device=DEV)
+        b.run("up_and_gate", lambda: [kernels_bf16.linear_bf16(h, w, up, False) for w in W], L, **mm(n_up, H))
+        mid = torch.empty(T, I, dtype=torch.bfloat16, device=DEV)
+        pq = torch.zeros(2, device=DEV)
+        b.run("xielu", lambda: [kernels.xielu(up[:, :I], pq, mid) for _ in range(L)], L, nbytes=T * I * 4)
+        W2 = [bf(H, I) for _ in range(L)]
+        b.run("down", lambda: [kernels_bf16.linear_bf16(mid, w, y32, False) for w in W2], L, **mm(H, I))
+    kernels_bf16.check_status()
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("mode", choices=["decode", "prefill"])
+    ap.add_argument("mode", choices=["decode", "prefill", "latent-decode", "latent-prefill"])
+    ap.add_argument("--rank", type=int, default=128, help="latent modes: cached numbers per token")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=3072)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -222,8 +316,11 @@ def main(argv=None) -> int:
     ap.add_argument("--once", action="store_true", help="launch without graph or timing (for profilers)")
     a = ap.parse_args(argv)
     if a.layers is None:
-        a.layers = 28 if a.mode == "decode" else 4
-    (decode if a.mode == "decode" else prefill)(a)
+        a.layers = 28 if a.mode.endswith("decode") else 4
+    if a.mode.startswith("latent"):
+        latent(a, a.mode == "latent-decode")
+    else:
+        (decode if a.mode == "decode" else prefill)(a)
     return 0
 
 

@@ -39,10 +39,14 @@ CONFIGS = {
     "r": _config(128, 500, 4, 1000, 7, 3, 11.3, 1e-6,
                  [_layer(4, 32, 32, 64, 256), _layer(4, 32, 32, 64, 256, kv_from=0),
                   _layer(2, 64, 64, 128, 192)]),
+    # ranks at or below the head sizes: bfloat16 multiplies the up-projections into the query and output
+    # matrices (both in layers 0 and 1, the keys' only in layer 2)
+    "t": _config(128, 200, 3, 64, 5, 9, 4.0, 1e-6,
+                 [_layer(4, 64, 48, 64, 160), _layer(2, 64, 64, 64, 96, kv_from=0), _layer(4, 64, 32, 64, None, kv_from=0)]),
     # a single tap (the convolution sees the token itself only), a width that is no multiple of 8
     "s": _config(60, 130, 1, 11, 3, 2, 2.0, 1e-6, [_layer(3, 12, 20, 36, 44), _layer(2, 10, 6, 20, None)]),
 }
-SEEDS = {"p": 11, "q": 12, "r": 13, "s": 14}
+SEEDS = {"p": 11, "q": 12, "r": 13, "s": 14, "t": 15}
 
 
 def make_weights(cfg: dict, seed: int) -> dict:
@@ -68,7 +72,7 @@ def make_weights(cfg: dict, seed: int) -> dict:
         W[p + "norm1"] = scale(d)
         W[p + "canon1"] = rng.standard_normal((d, taps)) * 0.5
         W[p + "rg1"], W[p + "rg1.b"] = mat(d, d), rng.standard_normal(d)
-        W[p + "mix.q"] = mat(H * dk, d, 3.0)
+        W[p + "mix.q"] = mat(H * dk, d, 2.0)
         if m.get("kv_from") is None:
             W[p + "mix.dkv"], W[p + "mix.dkv.norm"] = mat(r, d), scale(r)
         W[p + "mix.uk"], W[p + "mix.uv"] = mat(H * dk, r, 2.0), mat(H * dv, r)

@@ -125,24 +125,24 @@ def test_activation_gate_and_add():
     assert np.abs(normed.cpu().numpy() - SP.rms_norm(ref, w.astype(np.float64), 1e-5)).max() < 5e-6
 
 
+@pytest.mark.parametrize("heads,n,r", [(3, 10, 28), (2, 128, 96), (1, 40, 200)])
 @pytest.mark.parametrize("T", [1, 8, 13])
-def test_products_per_head(T):
+def test_products_per_head(T, heads, n, r):
     from gguf2bin_b200 import kernels
     rng = np.random.default_rng(T)
-    heads, n, r = 3, 10, 28
     w = rng.standard_normal((heads * n, r)).astype(np.float32)
     x = rng.standard_normal((T, heads * n + 5)).astype(np.float32)
     out = torch.empty((T, heads * r), dtype=torch.float32, device=DEV)
     kernels.head_product(dev(x)[:, :heads * n], dev(w), out, heads, False)
     ref = np.einsum("thn,hnr->thr", x[:, :heads * n].reshape(T, heads, n).astype(np.float64),
                     w.reshape(heads, n, r).astype(np.float64)).reshape(T, -1)
-    assert np.abs(out.cpu().numpy() - ref).max() < 2e-5
+    assert np.abs(out.cpu().numpy() - ref).max() < 1e-4
     a, gate = rng.standard_normal((T, heads * r)).astype(np.float32), rng.standard_normal((T, heads)).astype(np.float32)
     out2 = torch.empty((T, heads * n), dtype=torch.float32, device=DEV)
     kernels.head_product(dev(a), dev(w), out2, heads, True, dev(gate))
     ref2 = np.einsum("thr,hnr->thn", a.reshape(T, heads, r).astype(np.float64), w.reshape(heads, n, r).astype(np.float64))
     ref2 = (ref2 * SP.sigmoid(gate.astype(np.float64))[:, :, None]).reshape(T, -1)
-    assert np.abs(out2.cpu().numpy() - ref2).max() < 2e-5
+    assert np.abs(out2.cpu().numpy() - ref2).max() < 1e-4
 
 
 def _latent_attention_case(rank, heads, length, hot, dtype, decode):
@@ -196,7 +196,8 @@ def test_attention_over_latents_finds_a_far_key(rank, heads, dtype):
 # whole models
 # ----------------------------------------------------------------------------
 CASES = [(n, d) for n in CONFIGS for d in ("float32", "bfloat16")]
-LENGTHS = {"p": [70, 3, 130, 64, 1], "q": [129, 2, 40, 65], "r": [200, 33, 1, 128, 90], "s": [20, 65, 7]}
+LENGTHS = {"p": [70, 3, 130, 64, 1], "q": [129, 2, 40, 65], "r": [200, 33, 1, 128, 90], "s": [20, 65, 7],
+           "t": [150, 64, 9, 1]}
 
 
 @pytest.fixture(scope="module")
@@ -289,7 +290,16 @@ def test_unequal_batches_with_reuse(engines, name, dtype):
     assert eng.cache.table.pages.n_held == 0 and eng.cache.table.slots.n_held == 0
 
 
-@pytest.mark.parametrize("name,dtype", [("p", "float32"), ("r", "bfloat16"), ("q", "bfloat16")])
+def test_up_projections_folded_where_the_rank_allows(engines):
+    from gguf2bin_b200.parts.latent import FOLD_UP_TO
+    mixers = [b.mixer for b in engines("t", "bfloat16").model.blocks]
+    assert [(m.fold_k, m.fold_v) for m in mixers] == [(True, True), (True, True), (True, False)]
+    assert mixers[2].w_uk is None and mixers[2].w_uv is not None and mixers[1].w_in is not None
+    assert not any(b.mixer.fold_k or b.mixer.fold_v for b in engines("t", "float32").model.blocks)
+    assert not any(b.mixer.fold_k for b in engines("r", "bfloat16").model.blocks) and FOLD_UP_TO < 2
+
+
+@pytest.mark.parametrize("name,dtype", [("p", "float32"), ("r", "bfloat16"), ("q", "bfloat16"), ("t", "bfloat16")])
 def test_long_decoding(engines, name, dtype):
     """A short prompt, then 200 tokens one by one over three page borders, beside a second
     sequence that started elsewhere."""
