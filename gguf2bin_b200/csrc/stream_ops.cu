@@ -109,6 +109,7 @@ extern "C" int g2b_embed_pair_norm(const void *table, const void *pairs, int tab
 // thread takes eight neighbouring channels (16-byte loads) when the width allows, else one.
 // ---------------------------------------------------------------------------
 #define CANON_MAX_TAPS 16
+#define CANON_TOKENS 8        // tokens of a block in a long step, a warp each (their set-up is shared)
 
 template <typename TA> struct Vec8;
 template <> struct Vec8<bf16> {
@@ -148,23 +149,36 @@ template <typename TA, bool VEC>
 __global__ void __launch_bounds__(256)
 canon_conv_kernel(const TA *__restrict__ h, const float *__restrict__ w, const TA *__restrict__ ring,
                   const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
-                  const int *__restrict__ seq_slots, TA *__restrict__ out, int T, int H, int taps) {
+                  const int *__restrict__ seq_slots, TA *__restrict__ out, int T, int H, int taps,
+                  int per_block) {
   pdl_launch();
   pdl_wait();
-  __shared__ const TA *src[CANON_MAX_TAPS];           // the row that lies k steps back; nullptr: before the start
-  const int t = blockIdx.x;
-  if (threadIdx.x < taps) {
-    const int k = threadIdx.x, b = tok_seq[t], pos = tok_pos[t];
+  // the row that lies k steps back of each of the block's tokens; nullptr: before the start
+  __shared__ const TA *all_src[CANON_TOKENS][CANON_MAX_TAPS];
+  const int first = blockIdx.x * per_block;
+  for (int i = threadIdx.x; i < per_block * taps; i += blockDim.x) {
+    const int t = first + i / taps, k = i % taps;
     const TA *p = nullptr;
-    if (pos - k >= 0) {
-      if (t - k >= 0 && tok_seq[t - k] == b) p = h + (size_t)(t - k) * H;
-      else p = ring + ((size_t)seq_slots[b] * taps + (pos - k) % taps) * H;
+    if (t < T) {
+      const int b = tok_seq[t], pos = tok_pos[t];
+      if (pos - k >= 0) {
+        if (t - k >= 0 && tok_seq[t - k] == b) p = h + (size_t)(t - k) * H;
+        else p = ring + ((size_t)seq_slots[b] * taps + (pos - k) % taps) * H;
+      }
     }
-    src[k] = p;
+    all_src[i / taps][k] = p;
   }
   __syncthreads();
+  // one token per block: all threads on its row; several: a warp per token, so that every warp
+  // has its own row's loads in flight
+  const int ti = per_block > 1 ? (int)(threadIdx.x >> 5) : 0;
+  const int me = per_block > 1 ? (int)(threadIdx.x & 31) : (int)threadIdx.x;
+  const int team = per_block > 1 ? 32 : (int)blockDim.x;
+  const int t = first + ti;
+  if (ti >= per_block || t >= T) return;
+  const TA *const *src = all_src[ti];
   if (VEC) {
-    for (int j = 8 * threadIdx.x; j < H; j += 8 * blockDim.x) {
+    for (int j = 8 * me; j < H; j += 8 * team) {
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -183,7 +197,7 @@ canon_conv_kernel(const TA *__restrict__ h, const float *__restrict__ w, const T
       own.store(out + (size_t)t * H + j);
     }
   } else {
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    for (int j = me; j < H; j += team) {
       float acc = 0.f;
       for (int k = taps - 1; k >= 0; --k)
         if (src[k]) acc = fmaf(w[(size_t)j * taps + (taps - 1 - k)], to_f32(src[k][j]), acc);
@@ -201,18 +215,75 @@ extern "C" int g2b_canon_conv(const void *h, const float *w, const void *ring, i
   const int per = vec ? 8 : 1;
   int threads = (H / per + 31) / 32 * 32;
   threads = threads < 32 ? 32 : (threads > 256 ? 256 : threads);
+  const int per_block = T >= 256 ? CANON_TOKENS : 1;
+  if (per_block > 1) threads = 32 * CANON_TOKENS;
+  const dim3 grid((T + per_block - 1) / per_block);
   if (dtype == G2B_F32) {
     auto k = vec ? canon_conv_kernel<float, true> : canon_conv_kernel<float, false>;
-    g2b_launch(k, dim3(T), dim3(threads), 0, stream, (const float *)h, w, (const float *)ring, tok_pos,
-               tok_seq, seq_slots, (float *)out, T, H, taps);
+    g2b_launch(k, grid, dim3(threads), 0, stream, (const float *)h, w, (const float *)ring, tok_pos,
+               tok_seq, seq_slots, (float *)out, T, H, taps, per_block);
   } else if (dtype == G2B_BF16) {
     auto k = vec ? canon_conv_kernel<bf16, true> : canon_conv_kernel<bf16, false>;
-    g2b_launch(k, dim3(T), dim3(threads), 0, stream, (const bf16 *)h, w, (const bf16 *)ring, tok_pos,
-               tok_seq, seq_slots, (bf16 *)out, T, H, taps);
+    g2b_launch(k, grid, dim3(threads), 0, stream, (const bf16 *)h, w, (const bf16 *)ring, tok_pos,
+               tok_seq, seq_slots, (bf16 *)out, T, H, taps, per_block);
   } else {
     G2B_REFUSE("canon_conv: unknown dtype %d", dtype);
   }
   return g2b_check_launch("canon_conv");
+}
+
+// The same for a step of one token per sequence, with the norm in front of it and the ring's
+// update behind it in one launch: h = x / sqrt(mean(x^2) + eps) * g (rounded to the compute type,
+// as the other path stores it), u = h + conv(h) with the earlier rows from the ring, and h into
+// the ring at the token's position.  A slot's ring is read and written by its token's block only.
+template <typename TA>
+__global__ void __launch_bounds__(1024)
+norm_canon_single_kernel(const float *__restrict__ x, const float *__restrict__ g, float eps,
+                         const float *__restrict__ w, TA *__restrict__ ring,
+                         const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
+                         const int *__restrict__ seq_slots, TA *__restrict__ h_out,
+                         TA *__restrict__ u_out, int H, int taps) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  TA *my_ring = ring + (size_t)seq_slots[tok_seq[t]] * taps * H;
+  const float *xr = x + (size_t)t * H;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) ss = fmaf(xr[j], xr[j], ss);
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)H + eps);
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const TA hr = from_f32<TA>((g[j] * xr[j]) * inv);
+    const float hv = to_f32(hr);
+    float acc = 0.f;
+    for (int k = taps - 1; k >= 1; --k)               // oldest first; rows before the start are zero
+      if (pos - k >= 0) acc = fmaf(w[(size_t)j * taps + (taps - 1 - k)], to_f32(my_ring[(size_t)((pos - k) % taps) * H + j]), acc);
+    acc = fmaf(w[(size_t)j * taps + (taps - 1)], hv, acc);
+    h_out[(size_t)t * H + j] = hr;
+    u_out[(size_t)t * H + j] = from_f32<TA>(hv + acc);
+    if (taps > 1) my_ring[(size_t)(pos % taps) * H + j] = hr;
+  }
+}
+
+extern "C" int g2b_norm_canon_single(const float *x, const float *g, float eps, const float *w, void *ring,
+                                     int dtype, const int *tok_pos, const int *tok_seq,
+                                     const int *seq_slots, void *h_out, void *u_out, int T, int H,
+                                     int taps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (taps < 1 || taps > CANON_MAX_TAPS) G2B_REFUSE("norm_canon: %d taps outside 1..%d", taps, CANON_MAX_TAPS);
+  int threads = (H / 2 + 31) / 32 * 32;
+  threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+  if (dtype == G2B_F32)
+    g2b_launch(norm_canon_single_kernel<float>, dim3(T), dim3(threads), 0, stream, x, g, eps, w, (float *)ring,
+               tok_pos, tok_seq, seq_slots, (float *)h_out, (float *)u_out, H, taps);
+  else if (dtype == G2B_BF16)
+    g2b_launch(norm_canon_single_kernel<bf16>, dim3(T), dim3(threads), 0, stream, x, g, eps, w, (bf16 *)ring,
+               tok_pos, tok_seq, seq_slots, (bf16 *)h_out, (bf16 *)u_out, H, taps);
+  else
+    G2B_REFUSE("norm_canon: unknown dtype %d", dtype);
+  return g2b_check_launch("norm_canon");
 }
 
 // ---------------------------------------------------------------------------
@@ -403,32 +474,51 @@ extern "C" int g2b_head_product(const void *in, int in_stride, const void *W, co
   return g2b_check_launch("head_product");
 }
 
-// o[t, h, :] *= sigmoid(gate[t, h]); o [T, heads * n] contiguous
-template <typename TA>
-__global__ void head_gate_kernel(TA *__restrict__ o, const TA *__restrict__ gate, int gate_stride,
-                                 int heads, int n, long long total) {
+// o[t, h, :] *= sigmoid(gate[t, h]); o [T, heads * n] contiguous.  A block per token.
+template <typename TA, bool VEC>
+__global__ void __launch_bounds__(256)
+head_gate_kernel(TA *__restrict__ o, const TA *__restrict__ gate, int gate_stride, int heads, int n) {
   pdl_launch();
   pdl_wait();
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const long long th = i / n;                          // token * heads + head
-  const float g = to_f32(gate[(th / heads) * gate_stride + th % heads]);
-  o[i] = from_f32<TA>(to_f32(o[i]) * sigmoid_f(g));
+  extern __shared__ float hg_smem[];                  // sigmoid of the token's gates
+  const int t = blockIdx.x, W = heads * n;
+  for (int h = threadIdx.x; h < heads; h += blockDim.x)
+    hg_smem[h] = sigmoid_f(to_f32(gate[(size_t)t * gate_stride + h]));
+  __syncthreads();
+  TA *row = o + (size_t)t * W;
+  if (VEC) {                                           // n is a multiple of 8: a vector lies inside one head
+    for (int j = 8 * threadIdx.x; j < W; j += 8 * blockDim.x) {
+      Vec8<TA> v;
+      v.load(row + j);
+      const float g = hg_smem[j / n];
+      float r[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r[i] = v.get(i) * g;
+      v.set(r);
+      v.store(row + j);
+    }
+  } else {
+    for (int j = threadIdx.x; j < W; j += blockDim.x) row[j] = from_f32<TA>(to_f32(row[j]) * hg_smem[j / n]);
+  }
 }
 
 extern "C" int g2b_head_gate(void *o, const void *gate, int gate_stride, int T, int heads, int n,
                              int dtype, cudaStream_t stream) {
-  const long long total = (long long)T * heads * n;
-  if (total <= 0) return 0;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (dtype == G2B_F32)
-    g2b_launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float *)o, (const float *)gate,
-               gate_stride, heads, n, total);
-  else if (dtype == G2B_BF16)
-    g2b_launch(head_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16 *)o, (const bf16 *)gate,
-               gate_stride, heads, n, total);
-  else
+  if (T <= 0 || heads <= 0 || n <= 0) return 0;
+  const bool vec = n % 8 == 0 && ((uintptr_t)o & 15) == 0;
+  int threads = (heads * n / (vec ? 8 : 1) + 31) / 32 * 32;
+  threads = threads < 32 ? 32 : (threads > 256 ? 256 : threads);
+  const size_t smem = sizeof(float) * heads;
+  if (smem > 48 * 1024) G2B_REFUSE("head_gate: %d heads", heads);
+  if (dtype == G2B_F32) {
+    auto k = vec ? head_gate_kernel<float, true> : head_gate_kernel<float, false>;
+    g2b_launch(k, dim3(T), dim3(threads), smem, stream, (float *)o, (const float *)gate, gate_stride, heads, n);
+  } else if (dtype == G2B_BF16) {
+    auto k = vec ? head_gate_kernel<bf16, true> : head_gate_kernel<bf16, false>;
+    g2b_launch(k, dim3(T), dim3(threads), smem, stream, (bf16 *)o, (const bf16 *)gate, gate_stride, heads, n);
+  } else {
     G2B_REFUSE("head_gate: unknown dtype %d", dtype);
+  }
   return g2b_check_launch("head_gate");
 }
 
@@ -467,7 +557,8 @@ extern "C" int g2b_gated_add(float *x, const float *y, const void *g, int g_stri
                              int T, int H, const float *norm_w, float eps, void *normed, int dtype,
                              cudaStream_t stream) {
   if (T <= 0) return 0;
-  int threads = (H / 2 + 31) / 32 * 32;                // two elements a thread, up to 1,024 threads
+  // few rows (a decode step): two elements a thread, the row's latency is what counts; many rows: eight
+  int threads = (H / (T <= 256 ? 2 : 8) + 31) / 32 * 32;
   threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
   if (dtype == G2B_F32)
     g2b_launch(gated_add_kernel<float>, dim3(T), dim3(threads), 0, stream, x, y, (const float *)g, g_stride,
@@ -483,13 +574,21 @@ extern "C" int g2b_gated_add(float *x, const float *y, const void *g, int g_stri
 // ---------------------------------------------------------------------------
 // xIELU on the first F columns of a [T, stride] buffer
 // ---------------------------------------------------------------------------
+// exp(z) - 1 for z <= 0.  Where the result is rounded to bfloat16 the absolute error of
+// exp(z) - 1 by the fast exponential (1e-7) is far below half a unit of z / 2, the term beside it.
+template <typename TA> __device__ __forceinline__ float exp_minus_one(float z) { return expm1f(z); }
+template <> __device__ __forceinline__ float exp_minus_one<bf16>(float z) { return __expf(z) - 1.f; }
+
 template <typename TA, bool VEC>
 __global__ void __launch_bounds__(256)
 xielu_kernel(const TA *__restrict__ in, int in_stride, const float *__restrict__ pq,
              TA *__restrict__ out, int F) {
   pdl_launch();
   pdl_wait();
-  const float a = softplus_f(pq[0]), bq = 0.5f + softplus_f(pq[1]);
+  __shared__ float coef[2];
+  if (threadIdx.x < 2) coef[threadIdx.x] = (threadIdx.x ? 0.5f : 0.f) + softplus_f(pq[threadIdx.x]);
+  __syncthreads();
+  const float a = coef[0], bq = coef[1];
   const TA *row = in + (size_t)blockIdx.x * in_stride;           // rows along x: a step may have any number of them
   TA *orow = out + (size_t)blockIdx.x * F;
   if (VEC) {
@@ -501,7 +600,7 @@ xielu_kernel(const TA *__restrict__ in, int in_stride, const float *__restrict__
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float z = v.get(i);
-      r[i] = z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(bq, expm1f(z) - z, 0.5f * z);
+      r[i] = z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(bq, exp_minus_one<TA>(z) - z, 0.5f * z);
     }
     v.set(r);
     v.store(orow + j);

@@ -255,6 +255,22 @@ def canon_conv(h, w32, ring, ctx, out) -> None:
           _ptr(ctx.seq_slots), _ptr(out), T, H, w32.shape[1], _stream())
 
 
+def norm_canon_single(x32, norm_w, eps, w32, ring, ctx, h_out, u_out) -> None:
+    """A step of one token per sequence: h_out = rmsnorm(x32) * norm_w, u_out = h + convolution of h
+    with the earlier rows in ``ring``, and h into the ring at each token's position; one launch."""
+    _need(x32, torch.float32, "x")
+    _need(norm_w, torch.float32, "norm weight")
+    _need(w32, torch.float32, "convolution weight")
+    if ring.dtype != h_out.dtype or u_out.dtype != h_out.dtype or not (h_out.is_contiguous() and u_out.is_contiguous()):
+        raise KernelError("norm_canon_single: outputs and ring must have one dtype")
+    T, H = x32.shape
+    f = _fn("stream_ops.cu", "g2b_norm_canon_single",
+            [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_void_p])
+    _call(f, _ptr(x32), _ptr(norm_w), float(eps), _ptr(w32), _ptr(ring), _code(h_out.dtype), _ptr(ctx.tok_pos),
+          _ptr(ctx.tok_seq), _ptr(ctx.seq_slots), _ptr(h_out), _ptr(u_out), T, H, w32.shape[1], _stream())
+
+
 def latent_keep(d, norm_w, eps, pages, h, ring, taps, ctx) -> None:
     """Writes rmsnorm(d) * norm_w (d [T, rank], a view with any row stride; None: nothing) into
     the latent pages at the tokens' positions, and the last ``taps - 1`` rows of ``h`` of every

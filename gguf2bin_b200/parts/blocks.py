@@ -187,14 +187,22 @@ class GatedPreNormBlock:
         T, H, ws = x32.shape[0], self.hidden, ctx.workspace
         view = cache_view or {}
         h = ws.buffer("gated.normed", (T, H), self.dtype)
-        self.mixer_norm.forward(x32, h)
         u, keep = h, None
-        if self.taps:
+        w1 = getattr(self.mixer_norm, "weight", None)
+        if self.taps and ctx.all_single and isinstance(self.mixer_norm, RMSNorm) and w1 is not None:
+            # one token per sequence: norm, convolution and the ring's update in one launch
+            u = ws.buffer("gated.conv", (T, H), self.dtype)
+            ring = view["conv"].states if self.taps > 1 else h
+            kernels.norm_canon_single(x32, w1, self.mixer_norm.eps, self.w_conv, ring, ctx, h, u)
+        elif self.taps:
+            self.mixer_norm.forward(x32, h)
             ring = view["conv"].states if self.taps > 1 else h      # one tap: nothing before the token
             u = ws.buffer("gated.conv", (T, H), self.dtype)
             kernels.canon_conv(h, self.w_conv, ring, ctx, u)
             if self.taps > 1:
                 keep = (h, ring, self.taps)
+        else:
+            self.mixer_norm.forward(x32, h)
         gate = ws.buffer("gated.gate", (T, H), self.dtype)
         kernels.linear(h, self.g1, gate)
         y = ws.buffer("gated.result", (T, H), torch.float32)
