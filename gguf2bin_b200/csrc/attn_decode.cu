@@ -391,7 +391,7 @@ attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__
   for (int d = threadIdx.x; d < HD; d += COMBINE_WARPS * 32) {
     const float n = ((s_acc[0][d] + s_acc[1][d]) + s_acc[2][d]) + s_acc[3][d];
     float dn = ((s_acc[0][HD] + s_acc[1][HD]) + s_acc[2][HD]) + s_acc[3][HD];
-    if (sink) dn += exp2f(sink[th % nh] * LOG2E - M);          // a term without key or value, not scaled
+    if (sink) dn += exp2f(sink[th % nh] * LOG2E - M);          // the sink: a learned logit, taken as it is, that adds nothing to the sum
     out[th * HD + d] = __float2bfloat16_rn(n / dn);
   }
 }

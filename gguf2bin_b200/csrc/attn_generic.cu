@@ -13,8 +13,8 @@
 // only on its own position: not on how the tokens were cut into steps, nor on the batch.
 //
 // Two options for other kinds of attention.  `sink` (one float per query head, or null): the
-// softmax's denominator gets one more term exp(sink_h), which has no key and no value and is
-// not scaled.  `planes` = 1: a page holds one panel per kv head that serves as keys AND as
+// softmax's denominator is sum_j exp(s_j) + exp(sink_h): the sink takes probability, adds
+// nothing to the output, and is used as it is (the score scale does not apply).  `planes` = 1: a page holds one panel per kv head that serves as keys AND as
 // values (attention over cached latents); 2: a panel of keys and a panel of values.
 #include "common.cuh"
 

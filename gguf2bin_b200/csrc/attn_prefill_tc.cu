@@ -414,7 +414,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
         l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
         l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-        if (sink) {                                // one more term in the denominator: no key, no value, not scaled
+        if (sink) {                                // the sink: a learned logit that takes probability and adds nothing to the sum
           const float s2 = sink[h] * LOG2E;
           l_a += ex2(s2 - m_a);
           l_b += ex2(s2 - m_b);

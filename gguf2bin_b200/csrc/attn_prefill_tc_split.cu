@@ -411,7 +411,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const float l0 = g == 0 ? l : other.y, l1 = g == 0 ? other.y : l;
       const float mm = fmaxf(m0, m1);                          // finite for a row of the tile: it sees its own key
       const float a0 = m0 == -INFINITY ? 0.f : ex2(m0 - mm), a1 = m1 == -INFINITY ? 0.f : ex2(m1 - mm);
-      // with a sink: one more term in the denominator, without key or value and not scaled
+      // the sink: a learned logit per head that takes probability and adds nothing to the sum (taken as it is)
       const float inv = 1.f / (l0 * a0 + l1 * a1 + (sink ? ex2(sink[h] * LOG2E - mm) : 0.f));
       const float w0 = a0 * inv, w1 = a1 * inv;
       const bool two = n_pages > 1;                            // the second group has had pages

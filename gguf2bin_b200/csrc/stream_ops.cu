@@ -6,7 +6,8 @@
 //                     row(a, b) = (a * mul_prev + b * mul_cur) mod buckets; a sequence's first token
 //                     takes row `buckets`.  The previous token of a step's first token comes from a
 //                     two-place ring per slot that is indexed by position parity.
-//   canon_conv        u_t = h_t + sum_j w[:, j] * h_{t - taps + 1 + j} per channel, causal.  Rows before
+//   canon_conv        u_t = h_t + sum_j w[j, :] * h_{t - taps + 1 + j} per channel, causal (w is handed over
+//                     as [taps, width], a tap's weights side by side).  Rows before
 //                     the step's first come from a ring of `taps` rows per slot, indexed by
 //                     position mod taps; rows before the sequence's start are zero.
 //   latent_keep       c = rmsnorm(d) * w into the layer's latent page at the token's position, and
@@ -186,8 +187,10 @@ canon_conv_kernel(const TA *__restrict__ h, const float *__restrict__ w, const T
         if (!src[k]) continue;
         Vec8<TA> v;
         v.load(src[k] + j);
+        Vec8<float> wk;                                // the tap's weights of these eight channels
+        wk.load(w + (size_t)(taps - 1 - k) * H + j);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[(size_t)(j + i) * taps + (taps - 1 - k)], v.get(i), acc[i]);
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(wk.get(i), v.get(i), acc[i]);
       }
       Vec8<TA> own;
       own.load(src[0] + j);
@@ -200,7 +203,7 @@ canon_conv_kernel(const TA *__restrict__ h, const float *__restrict__ w, const T
     for (int j = me; j < H; j += team) {
       float acc = 0.f;
       for (int k = taps - 1; k >= 0; --k)
-        if (src[k]) acc = fmaf(w[(size_t)j * taps + (taps - 1 - k)], to_f32(src[k][j]), acc);
+        if (src[k]) acc = fmaf(w[(size_t)(taps - 1 - k) * H + j], to_f32(src[k][j]), acc);
       out[(size_t)t * H + j] = from_f32<TA>(to_f32(src[0][j]) + acc);
     }
   }
@@ -211,7 +214,7 @@ extern "C" int g2b_canon_conv(const void *h, const float *w, const void *ring, i
                               void *out, int T, int H, int taps, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (taps < 1 || taps > CANON_MAX_TAPS) G2B_REFUSE("canon_conv: %d taps outside 1..%d", taps, CANON_MAX_TAPS);
-  const bool vec = H % 8 == 0 && (((uintptr_t)h | (uintptr_t)ring | (uintptr_t)out) & 15) == 0;
+  const bool vec = H % 8 == 0 && (((uintptr_t)h | (uintptr_t)ring | (uintptr_t)out | (uintptr_t)w) & 15) == 0;
   const int per = vec ? 8 : 1;
   int threads = (H / per + 31) / 32 * 32;
   threads = threads < 32 ? 32 : (threads > 256 ? 256 : threads);
@@ -259,8 +262,8 @@ norm_canon_single_kernel(const float *__restrict__ x, const float *__restrict__ 
     const float hv = to_f32(hr);
     float acc = 0.f;
     for (int k = taps - 1; k >= 1; --k)               // oldest first; rows before the start are zero
-      if (pos - k >= 0) acc = fmaf(w[(size_t)j * taps + (taps - 1 - k)], to_f32(my_ring[(size_t)((pos - k) % taps) * H + j]), acc);
-    acc = fmaf(w[(size_t)j * taps + (taps - 1)], hv, acc);
+      if (pos - k >= 0) acc = fmaf(w[(size_t)(taps - 1 - k) * H + j], to_f32(my_ring[(size_t)((pos - k) % taps) * H + j]), acc);
+    acc = fmaf(w[(size_t)(taps - 1) * H + j], hv, acc);
     h_out[(size_t)t * H + j] = hr;
     u_out[(size_t)t * H + j] = from_f32<TA>(hv + acc);
     if (taps > 1) my_ring[(size_t)(pos % taps) * H + j] = hr;

@@ -241,7 +241,7 @@ def latent(a, single: bool) -> None:
     hb = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
     b.run("rmsnorm", lambda: [kernels.rmsnorm(x32, nw, 1e-6, hb) for _ in range(L)], L, nbytes=T * H * 6)
     ring = torch.zeros(B + 1, 3, H, dtype=torch.bfloat16, device=DEV)
-    cw = torch.randn(H, 3, device=DEV)
+    cw = torch.randn(3, H, device=DEV)
     b.run("canon_conv", lambda: [kernels.canon_conv(h, cw, ring, ctx, u) for _ in range(L)], L, nbytes=T * H * 4)
     if b.want("in_proj"):
         W = [bf(n_in, H) for _ in range(L)]

@@ -242,8 +242,8 @@ def embed_pair_norm(table, pairs, ids, ctx, ring, norm_w, eps, scale, buckets, m
 
 
 def canon_conv(h, w32, ring, ctx, out) -> None:
-    """out = h + causal convolution of h over time per channel; w32 float32 [width, taps];
-    ``ring`` [slots, taps, width]: the rows before the step, by position mod taps."""
+    """out = h + causal convolution of h over time per channel; w32 float32 [taps, width] (the
+    oldest tap first); ``ring`` [slots, taps, width]: the rows before the step, by position mod taps."""
     _need(w32, torch.float32, "convolution weight")
     if ring.dtype != h.dtype or out.dtype != h.dtype:
         raise KernelError("canon_conv: input, output and ring must have one dtype")
@@ -252,12 +252,13 @@ def canon_conv(h, w32, ring, ctx, out) -> None:
             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
              c_int, c_void_p])
     _call(f, _ptr(h), _ptr(w32), _ptr(ring), _code(h.dtype), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
-          _ptr(ctx.seq_slots), _ptr(out), T, H, w32.shape[1], _stream())
+          _ptr(ctx.seq_slots), _ptr(out), T, H, w32.shape[0], _stream())
 
 
 def norm_canon_single(x32, norm_w, eps, w32, ring, ctx, h_out, u_out) -> None:
     """A step of one token per sequence: h_out = rmsnorm(x32) * norm_w, u_out = h + convolution of h
-    with the earlier rows in ``ring``, and h into the ring at each token's position; one launch."""
+    (w32 float32 [taps, width]) with the earlier rows in ``ring``, and h into the ring at each token's
+    position; one launch."""
     _need(x32, torch.float32, "x")
     _need(norm_w, torch.float32, "norm weight")
     _need(w32, torch.float32, "convolution weight")
@@ -268,7 +269,7 @@ def norm_canon_single(x32, norm_w, eps, w32, ring, ctx, h_out, u_out) -> None:
             [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_void_p])
     _call(f, _ptr(x32), _ptr(norm_w), float(eps), _ptr(w32), _ptr(ring), _code(h_out.dtype), _ptr(ctx.tok_pos),
-          _ptr(ctx.tok_seq), _ptr(ctx.seq_slots), _ptr(h_out), _ptr(u_out), T, H, w32.shape[1], _stream())
+          _ptr(ctx.tok_seq), _ptr(ctx.seq_slots), _ptr(h_out), _ptr(u_out), T, H, w32.shape[0], _stream())
 
 
 def latent_keep(d, norm_w, eps, pages, h, ring, taps, ctx) -> None:

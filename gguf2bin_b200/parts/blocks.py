@@ -148,7 +148,8 @@ class GatedPreNormBlock:
         self.g1 = tensors[n["mixer_gate"]].contiguous()
         self.b1 = tensors[n["mixer_gate_bias"]].to(torch.float32).contiguous()
         if self.taps:
-            self.w_conv = tensors[n["conv"]].to(torch.float32).contiguous()
+            # stored [width, taps]; the kernels want a tap's weights side by side: [taps, width]
+            self.w_conv = tensors[n["conv"]].to(torch.float32).t().contiguous()
         if self.feed_forward is not None:
             self.ffn_norm.bind(tensors[n["ffn_norm"]])
             self.feed_forward.bind(tensors)

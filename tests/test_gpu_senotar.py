@@ -94,7 +94,7 @@ def test_convolution_over_steps(taps, dtype):
         ctx = step_ctx([n, n], [done, done], slots)
         rows = dev(np.concatenate([h[0][done:done + n], h[1][done:done + n]]), td)
         out = torch.empty_like(rows)
-        kernels.canon_conv(rows, dev(w), ring, ctx, out)
+        kernels.canon_conv(rows, dev(np.ascontiguousarray(w.T)), ring, ctx, out)
         kernels.latent_keep(None, None, 0.0, None, rows, ring if taps > 1 else None, taps, ctx)
         got[0].append(out[:n].float().cpu().numpy())
         got[1].append(out[n:].float().cpu().numpy())
