@@ -239,22 +239,34 @@ extern "C" int g2b_canon_conv(const void *h, const float *w, const void *ring, i
 // update behind it in one launch: h = x / sqrt(mean(x^2) + eps) * g (rounded to the compute type,
 // as the other path stores it), u = h + conv(h) with the earlier rows from the ring, and h into
 // the ring at the token's position.  A slot's ring is read and written by its token's block only.
+// With `y`: the gated addition that the layer in front left undone comes first, x += y * sigmoid(ga + gb).
 template <typename TA>
 __global__ void __launch_bounds__(1024)
-norm_canon_single_kernel(const float *__restrict__ x, const float *__restrict__ g, float eps,
+norm_canon_single_kernel(float *__restrict__ x, const float *__restrict__ g, float eps,
                          const float *__restrict__ w, TA *__restrict__ ring,
                          const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
                          const int *__restrict__ seq_slots, TA *__restrict__ h_out,
-                         TA *__restrict__ u_out, int H, int taps) {
+                         TA *__restrict__ u_out, int H, int taps, const float *__restrict__ y,
+                         const TA *__restrict__ ga, int ga_stride, const float *__restrict__ gb) {
   pdl_launch();
   pdl_wait();
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   TA *my_ring = ring + (size_t)seq_slots[tok_seq[t]] * taps * H;
-  const float *xr = x + (size_t)t * H;
+  float *xr = x + (size_t)t * H;
   float ss = 0.f;
-  for (int j = threadIdx.x; j < H; j += blockDim.x) ss = fmaf(xr[j], xr[j], ss);
+  if (y) {
+    const float *yr = y + (size_t)t * H;
+    const TA *gr = ga + (size_t)t * ga_stride;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+      const float v = fmaf(yr[j], sigmoid_f(to_f32(gr[j]) + (gb ? gb[j] : 0.f)), xr[j]);
+      xr[j] = v;                                       // read back below by the thread that wrote it
+      ss = fmaf(v, v, ss);
+    }
+  } else {
+    for (int j = threadIdx.x; j < H; j += blockDim.x) ss = fmaf(xr[j], xr[j], ss);
+  }
   ss = block_sum(ss, scratch);
   const float inv = 1.f / sqrtf(ss / (float)H + eps);
   for (int j = threadIdx.x; j < H; j += blockDim.x) {
@@ -270,20 +282,23 @@ norm_canon_single_kernel(const float *__restrict__ x, const float *__restrict__ 
   }
 }
 
-extern "C" int g2b_norm_canon_single(const float *x, const float *g, float eps, const float *w, void *ring,
+extern "C" int g2b_norm_canon_single(float *x, const float *g, float eps, const float *w, void *ring,
                                      int dtype, const int *tok_pos, const int *tok_seq,
                                      const int *seq_slots, void *h_out, void *u_out, int T, int H,
-                                     int taps, cudaStream_t stream) {
+                                     int taps, const float *y, const void *ga, int ga_stride,
+                                     const float *gb, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (taps < 1 || taps > CANON_MAX_TAPS) G2B_REFUSE("norm_canon: %d taps outside 1..%d", taps, CANON_MAX_TAPS);
   int threads = (H / 2 + 31) / 32 * 32;
   threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
   if (dtype == G2B_F32)
     g2b_launch(norm_canon_single_kernel<float>, dim3(T), dim3(threads), 0, stream, x, g, eps, w, (float *)ring,
-               tok_pos, tok_seq, seq_slots, (float *)h_out, (float *)u_out, H, taps);
+               tok_pos, tok_seq, seq_slots, (float *)h_out, (float *)u_out, H, taps, y, (const float *)ga,
+               ga_stride, gb);
   else if (dtype == G2B_BF16)
     g2b_launch(norm_canon_single_kernel<bf16>, dim3(T), dim3(threads), 0, stream, x, g, eps, w, (bf16 *)ring,
-               tok_pos, tok_seq, seq_slots, (bf16 *)h_out, (bf16 *)u_out, H, taps);
+               tok_pos, tok_seq, seq_slots, (bf16 *)h_out, (bf16 *)u_out, H, taps, y, (const bf16 *)ga,
+               ga_stride, gb);
   else
     G2B_REFUSE("norm_canon: unknown dtype %d", dtype);
   return g2b_check_launch("norm_canon");
@@ -553,7 +568,7 @@ gated_add_kernel(float *__restrict__ x, const float *__restrict__ y, const TA *_
   const float inv = 1.f / sqrtf(ss / (float)H + eps);
   TA *o = normed + (size_t)t * H;
   for (int j = threadIdx.x; j < H; j += blockDim.x)   // a thread reads back what it wrote itself
-    o[j] = from_f32<TA>((xr[j] * inv) * (norm_w ? norm_w[j] : 1.f));
+    o[j] = from_f32<TA>(((norm_w ? norm_w[j] : 1.f) * xr[j]) * inv);          // the order of the norm kernels
 }
 
 extern "C" int g2b_gated_add(float *x, const float *y, const void *g, int g_stride, const float *bias,

@@ -186,7 +186,10 @@ class Model:
             self.embedding.forward(ctx.tok_ids[:ctx.n_tokens], x, ctx, cache.view(len(self.spec.schedule)))
         else:
             self.embedding.forward(ctx.tok_ids[:ctx.n_tokens], x, ctx)
-        for position, entry in enumerate(self.spec.schedule):
+        schedule = self.spec.schedule
+        for position, entry in enumerate(schedule):
+            # a block may leave its last elementwise step to the next block's first launch
+            ctx.next_block = self.blocks[schedule[position + 1].layer] if position + 1 < len(schedule) else None
             self.blocks[entry.layer].forward(x, ctx, cache.view_for(position, self.spec.cache_owner(position)))
         if n_want == 0:
             return None

@@ -255,10 +255,11 @@ def canon_conv(h, w32, ring, ctx, out) -> None:
           _ptr(ctx.seq_slots), _ptr(out), T, H, w32.shape[0], _stream())
 
 
-def norm_canon_single(x32, norm_w, eps, w32, ring, ctx, h_out, u_out) -> None:
+def norm_canon_single(x32, norm_w, eps, w32, ring, ctx, h_out, u_out, add=None) -> None:
     """A step of one token per sequence: h_out = rmsnorm(x32) * norm_w, u_out = h + convolution of h
     (w32 float32 [taps, width]) with the earlier rows in ``ring``, and h into the ring at each token's
-    position; one launch."""
+    position; one launch.  ``add`` = (y32, gate, bias): x32 += y32 * sigmoid(gate + bias) first (a gated
+    addition that the layer in front left to this launch)."""
     _need(x32, torch.float32, "x")
     _need(norm_w, torch.float32, "norm weight")
     _need(w32, torch.float32, "convolution weight")
@@ -267,9 +268,16 @@ def norm_canon_single(x32, norm_w, eps, w32, ring, ctx, h_out, u_out) -> None:
     T, H = x32.shape
     f = _fn("stream_ops.cu", "g2b_norm_canon_single",
             [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_int, c_void_p])
+             c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    y = g = b = None
+    if add is not None:
+        y, g, b = add
+        _need(y, torch.float32, "y")
+        if g.dtype != h_out.dtype or g.stride(1) != 1:
+            raise KernelError("norm_canon_single: the gate must have the outputs' dtype and dense rows")
     _call(f, _ptr(x32), _ptr(norm_w), float(eps), _ptr(w32), _ptr(ring), _code(h_out.dtype), _ptr(ctx.tok_pos),
-          _ptr(ctx.tok_seq), _ptr(ctx.seq_slots), _ptr(h_out), _ptr(u_out), T, H, w32.shape[0], _stream())
+          _ptr(ctx.tok_seq), _ptr(ctx.seq_slots), _ptr(h_out), _ptr(u_out), T, H, w32.shape[0], _ptr(y), _ptr(g),
+          g.stride(0) if g is not None else 0, _ptr(b), _stream())
 
 
 def latent_keep(d, norm_w, eps, pages, h, ring, taps, ctx) -> None:

@@ -286,6 +286,8 @@ def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page
                    scale, sink=None, planes: int = 2) -> bool:
     if head_dim not in FAST_HEAD_SIZES or page_size != 64 or cache_pages.dtype != torch.bfloat16:
         return False
+    if not scale > 0.0:                      # the tensor-core kernels take the maximum before they scale
+        return False
     if ctx.all_single:
         attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale,
                     sink=sink, planes=planes)

@@ -60,6 +60,7 @@ class StepContext:
     attn_tiles_wide: Optional[torch.Tensor] = None   # the same with ATTN_WIDE_TILE_ROWS rows (tcgen05 kernel)
     n_attn_tiles_wide: int = 0
     step_cache: dict = field(default_factory=dict)   # tensors derived once per step (cleared by the model)
+    next_block: Optional[object] = None              # the block that runs after the one running now (None: the last)
 
     def rope_table(self, inv_freq: torch.Tensor) -> torch.Tensor:
         """(cos, sin) of every token's position times ``inv_freq``, computed once per step and

@@ -87,6 +87,9 @@ class PreNormBlock:
             self.feed_forward.forward(h, ctx, x32)
 
 
+PENDING = "gated_prenorm.owed"        # key of a step's left-over gated addition in StepContext.step_cache
+
+
 class GatedPreNormBlock:
     """``gated_prenorm``: h = norm(x); x += mixer(h + conv(h)) * sigmoid(G1 h + b1);
     h = norm(x); x += feed_forward(h) * sigmoid(G2 h + b2).
@@ -190,20 +193,27 @@ class GatedPreNormBlock:
         h = ws.buffer("gated.normed", (T, H), self.dtype)
         u, keep = h, None
         w1 = getattr(self.mixer_norm, "weight", None)
-        if self.taps and ctx.all_single and isinstance(self.mixer_norm, RMSNorm) and w1 is not None:
+        plain_norm = isinstance(self.mixer_norm, RMSNorm) and w1 is not None
+        # the last gated addition of the block in front, when it left that to this block's first launch
+        owed = ctx.step_cache.pop(PENDING, None)
+        if self.taps and ctx.all_single and plain_norm:
             # one token per sequence: norm, convolution and the ring's update in one launch
             u = ws.buffer("gated.conv", (T, H), self.dtype)
             ring = view["conv"].states if self.taps > 1 else h
-            kernels.norm_canon_single(x32, w1, self.mixer_norm.eps, self.w_conv, ring, ctx, h, u)
-        elif self.taps:
+            kernels.norm_canon_single(x32, w1, self.mixer_norm.eps, self.w_conv, ring, ctx, h, u, add=owed)
+            owed = None
+        elif owed is not None and plain_norm:
+            kernels.gated_add(x32, owed[0], owed[1], owed[2], w1, self.mixer_norm.eps, h)
+        else:
+            if owed is not None:
+                kernels.gated_add(x32, *owed)
             self.mixer_norm.forward(x32, h)
+        if self.taps and u is h:
             ring = view["conv"].states if self.taps > 1 else h      # one tap: nothing before the token
             u = ws.buffer("gated.conv", (T, H), self.dtype)
             kernels.canon_conv(h, self.w_conv, ring, ctx, u)
             if self.taps > 1:
                 keep = (h, ring, self.taps)
-        else:
-            self.mixer_norm.forward(x32, h)
         gate = ws.buffer("gated.gate", (T, H), self.dtype)
         kernels.linear(h, self.g1, gate)
         y = ws.buffer("gated.result", (T, H), torch.float32)
@@ -215,7 +225,7 @@ class GatedPreNormBlock:
             y.zero_()
             self.mixer.forward(u, ctx, view.get("mixer"), y)
         if self.feed_forward is None:
-            kernels.gated_add(x32, y, gate, self.b1)
+            self._add_or_leave(ctx, x32, y, gate, self.b1)
             return
         # the feed-forward's norm rides on the gated addition when it is a plain RMS norm
         eps = getattr(self.ffn_norm, "eps", None)
@@ -235,7 +245,17 @@ class GatedPreNormBlock:
             gate = ff.side_out
         else:
             kernels.linear(h, self.g2, gate)
-        kernels.gated_add(x32, y, gate, self.b2)
+        self._add_or_leave(ctx, x32, y, gate, self.b2)
+
+    @staticmethod
+    def _add_or_leave(ctx, x32, y, gate, bias) -> None:
+        """The block's last gated addition: left to the first launch of the next block of the schedule
+        when that is a block of this kind (``StepContext.next_block``, set by the model), which adds
+        while it reads the stream for its norm anyway; done here otherwise."""
+        if isinstance(getattr(ctx, "next_block", None), GatedPreNormBlock):
+            ctx.step_cache[PENDING] = (y, gate, bias)
+        else:
+            kernels.gated_add(x32, y, gate, bias)
 
 
 register_block("prenorm", PreNormBlock)

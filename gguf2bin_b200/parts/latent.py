@@ -14,9 +14,9 @@ that the schedule entry's ``cache_of`` layer stored), ``scale``.
 
 Scores, softmax and the latent's norm are 32-bit; products accumulate in 32-bit.
 
-Where a head's rank is not much more than its key (value) size, bfloat16 compute multiplies
-U_k into the query matrix (U_v into the output matrix) once, when the weights are bound
-(``FOLD_UP_TO``): the per-head products then cost nothing at run time, at the price of a query
+Where a head's rank is not much more than its key (value) size, or the matrices are small,
+bfloat16 compute multiplies U_k into the query matrix (U_v into the output matrix) once, when
+the weights are bound (``folds``): the per-head products then cost nothing at run time, at the price of a query
 (output) product that is rank / size times as large, and of one more rounding of the matrix to
 bfloat16.  The output gate is a number per head, so it commutes with U_v and is applied to
 the weighted latents.  The 32-bit path keeps the formula's order.
@@ -32,7 +32,20 @@ from ..weights.loader import Expected
 from .registry import register_mixer
 
 HEAD_PRODUCT_ROWS = 64       # steps of more rows multiply per head on the tensor cores (bfloat16)
-FOLD_UP_TO = 1.5             # rank / head size up to which an up-projection is multiplied into its neighbour
+FOLD_UP_TO = 1.5             # rank / head size up to which an up-projection is always multiplied into its neighbour
+FOLD_SMALL_UP_TO = 4.0       # ... and up to which it is while the matrix grows by no more than FOLD_SMALL_BYTES
+FOLD_SMALL_BYTES = 4 << 20
+
+
+def folds(rank: int, size: int, heads: int, width: int) -> bool:
+    """Whether a head's up-projection [size, rank] is multiplied into the [heads * size, width] matrix
+    beside it, which then has heads * rank rows.  Always while that costs at most half as much again;
+    for small matrices up to four times as much: a decode step reads the extra bytes in less time than
+    the launch of the per-head product takes, and a prompt's per-head products are one launch a head."""
+    if rank <= FOLD_UP_TO * size:
+        return True
+    extra = heads * (rank - size) * width * 2
+    return rank <= FOLD_SMALL_UP_TO * size and extra <= FOLD_SMALL_BYTES
 
 
 class LatentAttention:
@@ -81,8 +94,8 @@ class LatentAttention:
         n = self.names
         w_q, w_o = tensors[n["q"]], tensors[n["o"]]
         folding = self.dtype == torch.bfloat16 and w_q.dtype == torch.bfloat16 and w_o.dtype == torch.bfloat16
-        self.fold_k = folding and self.rank <= FOLD_UP_TO * self.dk
-        self.fold_v = folding and self.rank <= FOLD_UP_TO * self.dv
+        self.fold_k = folding and folds(self.rank, self.dk, self.nh, self.hidden)
+        self.fold_v = folding and folds(self.rank, self.dv, self.nh, self.hidden)
         parts = [] if self.fold_k else [w_q]
         if self.fold_k:
             # W_q'[h] = U_k[h]^T W_q[h]: [rank, qk_dim] x [qk_dim, width] per head

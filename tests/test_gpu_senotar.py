@@ -143,6 +143,18 @@ def test_products_per_head(T, heads, n, r):
     ref2 = np.einsum("thr,hnr->thn", a.reshape(T, heads, r).astype(np.float64), w.reshape(heads, n, r).astype(np.float64))
     ref2 = (ref2 * SP.sigmoid(gate.astype(np.float64))[:, :, None]).reshape(T, -1)
     assert np.abs(out2.cpu().numpy() - ref2).max() < 1e-4
+    # the same in bfloat16 storage (inputs that bfloat16 holds exactly; the output is rounded once)
+    wb, ab, gb = to_bf16_values(w), to_bf16_values(a), to_bf16_values(gate)
+    out3 = torch.empty((T, heads * n), dtype=torch.bfloat16, device=DEV)
+    kernels.head_product(dev(ab, torch.bfloat16), dev(wb, torch.bfloat16), out3, heads, True, dev(gb, torch.bfloat16))
+    ref3 = np.einsum("thr,hnr->thn", ab.reshape(T, heads, r).astype(np.float64), wb.reshape(heads, n, r).astype(np.float64))
+    ref3 = (ref3 * SP.sigmoid(gb.astype(np.float64))[:, :, None]).reshape(T, -1)
+    assert np.abs(out3.float().cpu().numpy() - ref3).max() <= 0.005 * np.abs(ref3).max() + 1e-3
+    xb = to_bf16_values(x[:, :heads * n])
+    out4 = torch.empty((T, heads * r), dtype=torch.bfloat16, device=DEV)
+    kernels.head_product(dev(xb, torch.bfloat16), dev(wb, torch.bfloat16), out4, heads, False)
+    ref4 = np.einsum("thn,hnr->thr", xb.reshape(T, heads, n).astype(np.float64), wb.reshape(heads, n, r).astype(np.float64))
+    assert np.abs(out4.float().cpu().numpy() - ref4.reshape(T, -1)).max() <= 0.005 * np.abs(ref4).max() + 1e-3
 
 
 def _latent_attention_case(rank, heads, length, hot, dtype, decode):
@@ -291,12 +303,16 @@ def test_unequal_batches_with_reuse(engines, name, dtype):
 
 
 def test_up_projections_folded_where_the_rank_allows(engines):
-    from gguf2bin_b200.parts.latent import FOLD_UP_TO
+    from gguf2bin_b200.parts.latent import folds
     mixers = [b.mixer for b in engines("t", "bfloat16").model.blocks]
-    assert [(m.fold_k, m.fold_v) for m in mixers] == [(True, True), (True, True), (True, False)]
-    assert mixers[2].w_uk is None and mixers[2].w_uv is not None and mixers[1].w_in is not None
+    assert [(m.fold_k, m.fold_v) for m in mixers] == [(True, True), (True, True), (True, True)]
+    assert mixers[2].w_uk is None and mixers[2].w_uv is None and mixers[1].w_in is not None
     assert not any(b.mixer.fold_k or b.mixer.fold_v for b in engines("t", "float32").model.blocks)
-    assert not any(b.mixer.fold_k for b in engines("r", "bfloat16").model.blocks) and FOLD_UP_TO < 2
+    # rank 64 over heads of 8 numbers: never folded; over heads of 40: folded while the model is small
+    q = [b.mixer for b in engines("q", "bfloat16").model.blocks]
+    assert (q[1].fold_k, q[1].fold_v) == (False, True) and (q[3].fold_k, q[3].fold_v) == (False, False)
+    assert folds(128, 128, 32, 4096) and folds(192, 128, 32, 4096) and not folds(512, 128, 32, 4096)
+    assert folds(128, 64, 16, 1024) and not folds(512, 64, 16, 1024) and not folds(256, 128, 32, 4096)
 
 
 @pytest.mark.parametrize("name,dtype", [("p", "float32"), ("r", "bfloat16"), ("q", "bfloat16"), ("t", "bfloat16")])
