@@ -17,7 +17,8 @@ from .csrc.build import KernelBuildError, KernelError, load_unit
 
 __all__ = ["KernelError", "KernelBuildError", "embed_rows", "rmsnorm", "qknorm_rope_cache",
            "rope_table", "cache_write", "swiglu", "advance_positions", "gemm_simt", "linear", "attn_generic",
-           "attention", "sample_rows", "sample_filtered", "recent_set", "seed_slots"]
+           "attention", "sample_rows", "sample_filtered", "recent_set", "seed_slots", "embed_pair_norm",
+           "canon_conv", "norm_canon_single", "latent_keep", "head_product", "head_gate", "gated_add", "xielu"]
 
 F32, BF16 = 0, 1
 EPI_STORE_F32, EPI_STORE_BF16, EPI_ACCUM_F32 = 0, 1, 2

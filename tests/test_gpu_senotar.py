@@ -199,7 +199,9 @@ def _latent_attention_case(rank, heads, length, hot, dtype, decode):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("rank,heads", [(24, 3), (64, 4), (128, 2), (64, 17)])
 def test_attention_over_latents_finds_a_far_key(rank, heads, dtype):
-    for length, hot in [(200, 0), (200, 63), (200, 64), (321, 127), (321, 128), (321, 319), (65, 64), (700, 5)]:
+    # page borders (64), the decode kernel's chunk borders (128, 256, 512), the first and the last key, far away
+    for length, hot in [(200, 0), (200, 63), (200, 64), (321, 127), (321, 128), (321, 319), (65, 64), (700, 5),
+                        (700, 255), (700, 256), (700, 511), (700, 512), (513, 512), (1, 0), (2, 0)]:
         _latent_attention_case(rank, heads, length, hot, dtype, decode=False)
         _latent_attention_case(rank, heads, length, hot, dtype, decode=True)
 
