@@ -77,9 +77,9 @@ struct Partial {
 
 // The query rows of a tile as A fragments: head = kvh * group + ht * 16 + row.
 __device__ __forceinline__ void load_q_tile(uint32_t (&qa)[KSTEPS][4], const bf16 *__restrict__ q, int t,
-                                            int nh, int kvh, int group, int ht, int g, int c) {
+                                            int q_stride, int kvh, int group, int ht, int g, int c) {
   const int row0 = ht * 16 + g, row1 = row0 + 8;
-  const bf16 *q0 = q + ((size_t)t * nh + (size_t)kvh * group + row0) * HD;
+  const bf16 *q0 = q + (size_t)t * q_stride + ((size_t)kvh * group + row0) * HD;
   const bf16 *q1 = q0 + 8 * HD;
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -240,7 +240,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
                    const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
                    const int *__restrict__ page_table, int P, int nh, int nkv, int window,
                    float scale_log2, float *__restrict__ part_o, float2 *__restrict__ part_ml,
-                   int n_chunks, int planes) {
+                   int n_chunks, int planes, int q_stride) {
   pdl_launch();
   extern __shared__ __align__(128) unsigned char smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -305,7 +305,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
   }
 
   uint32_t qa[KSTEPS][4];
-  load_q_tile(qa, q, t, nh, kvh, group, ht, g, c);
+  load_q_tile(qa, q, t, q_stride, kvh, group, ht, g, c);
   Partial acc;
   clear_partial(acc);
   attend_pages(acc, qa, k_smem, v_smem, pg0, WARPS, n_pages, pos, lo, scale_log2, lane, panel_of);
@@ -335,7 +335,8 @@ constexpr int COMBINE_WARPS = 4;
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
                     const int *__restrict__ tok_pos, int nh, int window, int n_chunks,
-                    bf16 *__restrict__ out, const float *__restrict__ sink) {
+                    bf16 *__restrict__ out, const float *__restrict__ sink,
+                    const bf16 *__restrict__ gate, int gate_stride) {
   pdl_launch();
   pdl_wait();
   __shared__ float s_max[COMBINE_WARPS];
@@ -392,6 +393,8 @@ attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__
     const float n = ((s_acc[0][d] + s_acc[1][d]) + s_acc[2][d]) + s_acc[3][d];
     float dn = ((s_acc[0][HD] + s_acc[1][HD]) + s_acc[2][HD]) + s_acc[3][HD];
     if (sink) dn += exp2f(sink[th % nh] * LOG2E - M);          // the sink: a learned logit, taken as it is, that adds nothing to the sum
+    // with a gate: the head's output times sigmoid(gate), i.e. the denominator times (1 + exp(-gate))
+    if (gate) dn *= 1.f + __expf(-__bfloat162float(gate[(size_t)t * gate_stride + th % nh]));
     out[th * HD + d] = __float2bfloat16_rn(n / dn);
   }
 }
@@ -407,9 +410,11 @@ extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, cons
                                const int *tok_seq, const int *page_table, int P, int T, int nh,
                                int nkv, int hd, int page_size, int window, float scale,
                                int max_kv_len, float *part_o, float *part_ml,
-                               const float *sink, int planes, cudaStream_t stream) {
+                               const float *sink, int planes, int q_stride, const void *gate,
+                               int gate_stride, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (planes != 1 && planes != 2) G2B_REFUSE("attn_decode: %d panels per page and kv head (1 or 2)", planes);
+  if (q_stride < nh * hd || q_stride % 2) G2B_REFUSE("attn_decode: query rows %d elements apart", q_stride);
   if (hd != HD) G2B_REFUSE("attn_decode: built for head_dim %d, got %d", HD, hd);
   if (page_size != PAGE) G2B_REFUSE("attn_decode: page size must be %d, got %d", PAGE, page_size);
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_decode: %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -430,11 +435,12 @@ extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, cons
   dim3 grid(n_chunks, nkv * head_tiles, T);
   g2b_launch(attn_decode_kernel, dim3(grid), dim3(WARPS * 32), smem, stream, 
       (const bf16 *)q, (const bf16 *)cache, tok_pos, tok_seq, page_table, P, nh, nkv, window,
-      scale * LOG2E, part_o, (float2 *)part_ml, n_chunks, planes);
+      scale * LOG2E, part_o, (float2 *)part_ml, n_chunks, planes, q_stride);
   int rc = g2b_check_launch("attn_decode");
   if (rc) return rc;
   g2b_launch(attn_combine_kernel, dim3((unsigned)((size_t)T * nh)), dim3(COMBINE_WARPS * 32), 0, stream, 
-      part_o, (const float2 *)part_ml, tok_pos, nh, window, n_chunks, (bf16 *)out, sink);
+      part_o, (const float2 *)part_ml, tok_pos, nh, window, n_chunks, (bf16 *)out, sink, (const bf16 *)gate,
+      gate_stride);
   return g2b_check_launch("attn_combine");
 }
 

@@ -54,5 +54,6 @@ extern "C" int g2b_attn_decode_noalloc(const void *q, void *out, const void *cac
   float *part_o = scratch;                                    // slots * HD floats
   float *part_ml = scratch + (size_t)slots * HD;              // slots * 2 floats (8-byte aligned)
   return g2b_attn_decode(q, out, cache, tok_pos, tok_seq, page_table, P, T, n_heads, n_kv_heads,
-                         head_dim, page_size, window, scale, max_kv_len, part_o, part_ml, nullptr, 2, stream);
+                         head_dim, page_size, window, scale, max_kv_len, part_o, part_ml, nullptr, 2, n_heads * head_dim,
+                         nullptr, 0, stream);
 }

@@ -16,6 +16,9 @@
 // softmax's denominator is sum_j exp(s_j) + exp(sink_h): the sink takes probability, adds
 // nothing to the output, and is used as it is (the score scale does not apply).  `planes` = 1: a page holds one panel per kv head that serves as keys AND as
 // values (attention over cached latents); 2: a panel of keys and a panel of values.
+// `q_stride`: elements between the query rows of two tokens (the queries may be columns of a wider
+// product's output).  `gate` (one number per token and head, or null): the head's output is
+// multiplied by its sigmoid.
 #include "common.cuh"
 
 G2B_DEFINE_LAST_ERROR
@@ -29,7 +32,8 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
                     const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
                     const int *__restrict__ page_table, int P, int n_tokens, int nh, int nkv,
                     int hd, int page_size, int window, float scale,
-                    const float *__restrict__ sink, int planes) {
+                    const float *__restrict__ sink, int planes, int q_stride,
+                    const T *__restrict__ gate, int gate_stride) {
   pdl_launch();
   pdl_wait();
   __shared__ float qs[AG_WARPS][AG_MAX_HD];
@@ -41,7 +45,7 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
   const int kvh = h / (nh / nkv);
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
 
-  const T *qp = q + (size_t)t * nh * hd + (size_t)h * hd;
+  const T *qp = q + (size_t)t * q_stride + (size_t)h * hd;
   for (int j = lane; j < hd; j += 32) qs[warp][j] = to_f32(qp[j]);
   __syncwarp();
 
@@ -86,7 +90,8 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
   }
   T *op = out + (size_t)t * nh * hd + (size_t)h * hd;
   if (sink) l += expf(sink[h] - m);                                // m is finite: the token's own key
-  const float inv_l = 1.f / l;
+  float inv_l = 1.f / l;
+  if (gate) inv_l *= 1.f / (1.f + expf(-to_f32(gate[(size_t)t * gate_stride + h])));   // the head's output gate
 #pragma unroll
   for (int i = 0; i < AG_MAX_HD / 32; ++i) {
     const int d = lane + 32 * i;
@@ -97,8 +102,8 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
 extern "C" int g2b_attn_generic(const void *q, void *out, int dtype, const void *cache,
                                 const int *tok_pos, const int *tok_seq, const int *page_table,
                                 int P, int n_tokens, int nh, int nkv, int hd, int page_size,
-                                int window, float scale, const float *sink, int planes,
-                                cudaStream_t stream) {
+                                int window, float scale, const float *sink, int planes, int q_stride,
+                                const void *gate, int gate_stride, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (planes != 1 && planes != 2) G2B_REFUSE("attn_generic: %d panels per page and kv head (1 or 2)", planes);
   if (hd <= 0 || hd > AG_MAX_HD) G2B_REFUSE("attn_generic: head_dim %d outside 1..%d", hd, AG_MAX_HD);
@@ -110,11 +115,11 @@ extern "C" int g2b_attn_generic(const void *q, void *out, int dtype, const void 
   if (dtype == G2B_F32)
     g2b_launch(attn_generic_kernel<float>, dim3(blocks), dim3(AG_WARPS * 32), 0, stream, 
         (const float *)q, (float *)out, (const float *)cache, tok_pos, tok_seq, page_table, P,
-        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes);
+        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes, q_stride, (const float *)gate, gate_stride);
   else if (dtype == G2B_BF16)
     g2b_launch(attn_generic_kernel<bf16>, dim3(blocks), dim3(AG_WARPS * 32), 0, stream, 
         (const bf16 *)q, (bf16 *)out, (const bf16 *)cache, tok_pos, tok_seq, page_table, P,
-        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes);
+        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes, q_stride, (const bf16 *)gate, gate_stride);
   else
     G2B_REFUSE("attn_generic: unknown dtype %d", dtype);
   return g2b_check_launch("attn_generic");

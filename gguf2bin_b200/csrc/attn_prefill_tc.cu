@@ -122,7 +122,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_kv, bf16 *__restrict__ out,
                        const int4 *__restrict__ tiles, const int *__restrict__ page_table, int P,
                        int nh, int nkv, int window, float scale_log2, int first_wave,
-                       int *__restrict__ status, const float *__restrict__ sink, int planes) {
+                       int *__restrict__ status, const float *__restrict__ sink, int planes,
+                       const bf16 *__restrict__ gate, int gate_stride) {
   pdl_launch();
   // The swizzled panels need 1024-byte alignment.  The kernel has no static shared memory, so
   // the dynamic part starts at the aligned base of the window; checked rather than assumed.
@@ -419,7 +420,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           l_a += ex2(s2 - m_a);
           l_b += ex2(s2 - m_b);
         }
-        const float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
+        float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
+        if (gate) {                                // the head's output gate: times sigmoid(gate[token, head])
+          if (rA < n_rows) inv_a /= 1.f + __expf(-__bfloat162float(gate[(size_t)(t0 + rA) * gate_stride + h]));
+          if (rB < n_rows) inv_b /= 1.f + __expf(-__bfloat162float(gate[(size_t)(t0 + rB) * gate_stride + h]));
+        }
         bf16 *op_a = out + ((size_t)(t0 + rA) * nh + h) * HD + 2 * c;
         bf16 *op_b = out + ((size_t)(t0 + rB) * nh + h) * HD + 2 * c;
 #pragma unroll 1
@@ -453,21 +458,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, long long n_cache_pages,
                                    const int *tiles, int n_tiles, const int *page_table, int P,
                                    int T, int nh, int nkv, int hd, int page_size, int window,
-                                   float scale, const float *sink, int planes, int *status,
-                                   cudaStream_t stream) {
+                                   float scale, const float *sink, int planes, int q_stride,
+                                   const void *gate, int gate_stride, int *status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (hd != HD) G2B_REFUSE("attn_prefill_tc: built for head_dim %d, got %d", HD, hd);
   if (page_size != PAGE) G2B_REFUSE("attn_prefill_tc: page size must be %d, got %d", PAGE, page_size);
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_prefill_tc: %d heads are not a multiple of %d kv heads", nh, nkv);
   if ((long long)n_tiles * nh > 0x7fffffffLL) G2B_REFUSE("attn_prefill_tc: %d tiles x %d heads", n_tiles, nh);
   if (!status) G2B_REFUSE("attn_prefill_tc: no status word");
+  if (q_stride < nh * HD || q_stride % 8) G2B_REFUSE("%s: query rows %d elements apart", "attn_prefill_tc", q_stride);
   if (planes != 1 && planes != 2) G2B_REFUSE("attn_prefill_tc: %d panels per page and kv head (1 or 2)", planes);
   if (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15)
     G2B_REFUSE("attn_prefill_tc: q, out and the cache must be 16-byte aligned");
   if (n_cache_pages * planes * nkv * PAGE > 0x7fffffffLL)
     G2B_REFUSE("attn_prefill_tc: the cache layer has too many rows for 32-bit copy coordinates");
   CUtensorMap mq, mkv;
-  int rc = get_map(&mq, q, T, nh * HD, nh * HD, BM);
+  int rc = get_map(&mq, q, T, nh * HD, q_stride, BM);
   if (rc) G2B_REFUSE("attn_prefill_tc: tensor map of q failed (%d)", rc);
   rc = get_map(&mkv, cache, n_cache_pages * planes * nkv * PAGE, HD, HD, PAGE);
   if (rc) G2B_REFUSE("attn_prefill_tc: tensor map of the cache failed (%d)", rc);
@@ -485,7 +491,7 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
     if (cfg_dev >= 0) configured.value[cfg_dev] = n_sms;
   }
   g2b_launch(attn_prefill_tc_kernel, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
-             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status, sink, planes);
+             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status, sink, planes, (const bf16 *)gate, gate_stride);
   return g2b_check_launch("attn_prefill_tc");
 }
 

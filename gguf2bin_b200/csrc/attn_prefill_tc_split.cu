@@ -139,7 +139,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_kv, bf16 *__restrict__ out,
                        const int4 *__restrict__ tiles, const int *__restrict__ page_table, int P,
                        int nh, int nkv, int window, float scale_log2, int *__restrict__ status,
-                       const float *__restrict__ sink, int planes) {
+                       const float *__restrict__ sink, int planes,
+                       const bf16 *__restrict__ gate, int gate_stride) {
   pdl_launch();
   // The swizzled panels need 1024-byte alignment.  The kernel has no static shared memory, so
   // the dynamic part starts at the aligned base of the window; checked rather than assumed.
@@ -412,7 +413,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const float mm = fmaxf(m0, m1);                          // finite for a row of the tile: it sees its own key
       const float a0 = m0 == -INFINITY ? 0.f : ex2(m0 - mm), a1 = m1 == -INFINITY ? 0.f : ex2(m1 - mm);
       // the sink: a learned logit per head that takes probability and adds nothing to the sum (taken as it is)
-      const float inv = 1.f / (l0 * a0 + l1 * a1 + (sink ? ex2(sink[h] * LOG2E - mm) : 0.f));
+      float inv = 1.f / (l0 * a0 + l1 * a1 + (sink ? ex2(sink[h] * LOG2E - mm) : 0.f));
+      // the head's output gate: times sigmoid(gate[token, head])
+      if (gate && row < n_rows) inv /= 1.f + __expf(-__bfloat162float(gate[(size_t)(t0 + row) * gate_stride + h]));
       const float w0 = a0 * inv, w1 = a1 * inv;
       const bool two = n_pages > 1;                            // the second group has had pages
       // group g writes columns [g HD / 2, (g + 1) HD / 2) of the row
@@ -453,21 +456,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, long long n_cache_pages,
                                    const int *tiles, int n_tiles, const int *page_table, int P,
                                    int T, int nh, int nkv, int hd, int page_size, int window,
-                                   float scale, const float *sink, int planes, int *status,
-                                   cudaStream_t stream) {
+                                   float scale, const float *sink, int planes, int q_stride,
+                                   const void *gate, int gate_stride, int *status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (hd != HD) G2B_REFUSE("attn_prefill_tc (split): built for head_dim %d, got %d", HD, hd);
   if (page_size != PAGE) G2B_REFUSE("attn_prefill_tc (split): page size must be %d, got %d", PAGE, page_size);
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_prefill_tc (split): %d heads are not a multiple of %d kv heads", nh, nkv);
   if ((long long)n_tiles * nh > 0x7fffffffLL) G2B_REFUSE("attn_prefill_tc (split): %d tiles x %d heads", n_tiles, nh);
   if (!status) G2B_REFUSE("attn_prefill_tc (split): no status word");
+  if (q_stride < nh * HD || q_stride % 8) G2B_REFUSE("%s: query rows %d elements apart", "attn_prefill_tc (split)", q_stride);
   if (planes != 1 && planes != 2) G2B_REFUSE("attn_prefill_tc (split): %d panels per page and kv head (1 or 2)", planes);
   if (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15)
     G2B_REFUSE("attn_prefill_tc (split): q, out and the cache must be 16-byte aligned");
   if (n_cache_pages * planes * nkv * PAGE > 0x7fffffffLL)
     G2B_REFUSE("attn_prefill_tc (split): the cache layer has too many rows for 32-bit copy coordinates");
   CUtensorMap mq, mkv;
-  int rc = get_map(&mq, q, T, nh * HD, nh * HD, BM);
+  int rc = get_map(&mq, q, T, nh * HD, q_stride, BM);
   if (rc) G2B_REFUSE("attn_prefill_tc (split): tensor map of q failed (%d)", rc);
   rc = get_map(&mkv, cache, n_cache_pages * planes * nkv * PAGE, HD, HD, PAGE);
   if (rc) G2B_REFUSE("attn_prefill_tc (split): tensor map of the cache failed (%d)", rc);
@@ -481,7 +485,7 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
     if (cfg_dev >= 0) configured.value[cfg_dev] = 1;
   }
   g2b_launch(attn_prefill_tc_kernel, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
-             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, status, sink, planes);
+             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, status, sink, planes, (const bf16 *)gate, gate_stride);
   return g2b_check_launch("attn_prefill_tc (split)");
 }
 

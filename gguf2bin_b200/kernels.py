@@ -436,33 +436,38 @@ def attention_notices(what: str, head_dim: int, page_size: int, compute_dtype: t
 # attention
 # ---------------------------------------------------------------------------
 def attn_generic(q, out, cache_pages, tok_pos, tok_seq, page_table, n_heads, n_kv_heads,
-                 head_dim, page_size, window, scale, sink=None, planes: int = 2) -> None:
+                 head_dim, page_size, window, scale, sink=None, planes: int = 2, gate=None) -> None:
     """Causal attention of every token of the step over its sequence's cache pages,
-    32-bit arithmetic; q, out [T, n_heads*head_dim].  ``sink`` (float32 [n_heads]): one more
+    32-bit arithmetic; q [T, n_heads*head_dim] (rows may lie further apart: columns of a wider
+    buffer), out [T, n_heads*head_dim] contiguous.  ``sink`` (float32 [n_heads]): one more
     term exp(sink_h) in each head's softmax denominator.  ``planes`` = 1: the pages hold one
-    panel per kv head that is read as keys and as values."""
+    panel per kv head that is read as keys and as values.  ``gate`` [T, n_heads] (rows may lie
+    further apart): every head's output is multiplied by the sigmoid of its gate."""
     f = _fn("attn_generic.cu", "g2b_attn_generic",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p])
     if q.dtype != cache_pages.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, out and the cache must have one dtype")
+    if q.stride(1) != 1 or not out.is_contiguous() or (gate is not None and (gate.stride(1) != 1 or gate.dtype != q.dtype)):
+        raise KernelError("attention: q and gate need dense rows, out must be contiguous, gate of q's dtype")
     if sink is not None:
         _need(sink, torch.float32, "sink")
     _call(f, _ptr(q), _ptr(out), _code(q.dtype), _ptr(cache_pages), _ptr(tok_pos), _ptr(tok_seq),
           _ptr(page_table), page_table.shape[1], q.shape[0], n_heads, n_kv_heads, head_dim,
-          page_size, window, scale, _ptr(sink), planes, _stream())
+          page_size, window, scale, _ptr(sink), planes, q.stride(0), _ptr(gate),
+          gate.stride(0) if gate is not None else 0, _stream())
 
 
 def attention(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-              scale, sink=None, planes: int = 2) -> None:
+              scale, sink=None, planes: int = 2, gate=None) -> None:
     """Attention of a step: the tensor-core kernels when they take the case, else the
-    32-bit kernel."""
+    32-bit kernel.  ``q`` and ``gate`` may be column ranges of a wider buffer."""
     if q.dtype == torch.bfloat16:
         if (_bf16 or _bf16_mod()).attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim,
-                                       page_size, window, scale, sink, planes):
+                                       page_size, window, scale, sink, planes, gate):
             return
     attn_generic(q, out, cache_pages, ctx.tok_pos, ctx.tok_seq, ctx.page_table, n_heads,
-                 n_kv_heads, head_dim, page_size, window, scale, sink, planes)
+                 n_kv_heads, head_dim, page_size, window, scale, sink, planes, gate)
 
 
 def normed_product(x32, eps, w, out, gate_block=None) -> bool:

@@ -283,20 +283,25 @@ def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, bl
 
 
 def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                   scale, sink=None, planes: int = 2) -> bool:
+                   scale, sink=None, planes: int = 2, gate=None) -> bool:
     if head_dim not in FAST_HEAD_SIZES or page_size != 64 or cache_pages.dtype != torch.bfloat16:
+        return False
+    if q.stride(1) != 1 or q.stride(0) % 8 or q.data_ptr() % 16 or not out.is_contiguous():
+        return False
+    if gate is not None and (gate.dtype != torch.bfloat16 or gate.stride(1) != 1):
         return False
     if not scale > 0.0:                      # the tensor-core kernels take the maximum before they scale
         return False
     if ctx.all_single:
         attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale,
-                    sink=sink, planes=planes)
+                    sink=sink, planes=planes, gate=gate)
         return True
     if USE_TC_ATTENTION and getattr(ctx, "attn_tiles_wide", None) is not None and ctx.n_attn_tiles_wide > 0:
         attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale,
-                        sink=sink, planes=planes)
+                        sink=sink, planes=planes, gate=gate)
         return True
-    if sink is not None or planes != 2:      # the mma.sync prompt kernel knows neither
+    if sink is not None or planes != 2 or gate is not None or q.stride(0) != n_heads * head_dim:
+        # the mma.sync prompt kernel knows none of these
         return False
     if getattr(ctx, "attn_tiles", None) is not None and ctx.n_attn_tiles > 0:
         attn_prefill(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale)
@@ -308,7 +313,7 @@ USE_TC_ATTENTION = True      # prompt attention on tcgen05 (else the mma.sync ke
 
 
 def attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                    scale, defines=(), split=None, sink=None, planes: int = 2) -> None:
+                    scale, defines=(), split=None, sink=None, planes: int = 2, gate=None) -> None:
     """Prompt attention on the tcgen05 tensor cores over the step's 128-row query tiles.  Two
     kernels with the same interface: two CTAs per SM, a tile each (``attn_prefill_tc.cu``), and
     one CTA per SM whose two softmax groups share a tile's pages (``attn_prefill_tc_split.cu``;
@@ -323,12 +328,12 @@ def attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, pag
         split = items <= sms or (items <= 2 * sms and getattr(ctx, "max_kv_len", 0) >= 1024)
     f = _fn("attn_prefill_tc_split.cu" if split else "attn_prefill_tc.cu", "g2b_attn_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p],
+             c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p],
             defines=(f"HD={head_dim}",) + tuple(defines))
     _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), cache_pages.shape[0], _ptr(ctx.attn_tiles_wide),
           ctx.n_attn_tiles_wide, _ptr(ctx.page_table), ctx.page_table.shape[1], q.shape[0], n_heads,
-          n_kv_heads, head_dim, page_size, window, scale, _ptr(sink), planes, _ptr(_status_word(q.device)),
-          _stream())
+          n_kv_heads, head_dim, page_size, window, scale, _ptr(sink), planes, q.stride(0), _ptr(gate),
+          gate.stride(0) if gate is not None else 0, _ptr(_status_word(q.device)), _stream())
 
 
 def attn_prefill(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
@@ -366,7 +371,7 @@ def decode_chunk_pages(units: int, pages: int, head_dim: int, slots: int) -> int
 
 
 def attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                scale, fine=None, pages=None, sink=None, planes: int = 2) -> None:
+                scale, fine=None, pages=None, sink=None, planes: int = 2, gate=None) -> None:
     """One token per sequence: split-key attention with partial results in scratch memory
     and a combine pass.  A CTA takes a chunk of keys of one kv head: 256 as a rule, 128, 384 or
     512 where ``decode_chunk_pages`` says so (``fine`` = 128; ``pages`` = pages of 64 keys per
@@ -390,10 +395,11 @@ def attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_si
     part_ml = ws.buffer("attn.part_ml", (T * n_heads * n_chunks * 2,), torch.float32)
     f = _fn("attn_decode.cu", "g2b_attn_decode",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+             c_int, c_void_p],
             defines=defines)
     _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
           _ptr(ctx.page_table), ctx.page_table.shape[1], T, n_heads, n_kv_heads, head_dim,
           page_size, window, scale, int(ctx.max_kv_len), _ptr(part_o), _ptr(part_ml), _ptr(sink), planes,
-          _stream())
+          q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
     kernels.count_launches(1)                      # the attention and the merge of its chunks

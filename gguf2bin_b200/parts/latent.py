@@ -19,7 +19,8 @@ bfloat16 compute multiplies U_k into the query matrix (U_v into the output matri
 the weights are bound (``folds``): the per-head products then cost nothing at run time, at the price of a query
 (output) product that is rank / size times as large, and of one more rounding of the matrix to
 bfloat16.  The output gate is a number per head, so it commutes with U_v and is applied to
-the weighted latents.  The 32-bit path keeps the formula's order.
+the weighted latents, by the attention kernel itself; the queries, which then come out of the
+input product in latent coordinates, are read by the attention in place.  The 32-bit path keeps the formula's order.
 """
 from __future__ import annotations
 
@@ -71,7 +72,6 @@ class LatentAttention:
         self.n_c = 0 if self.shared_kv else self.rank
         self.n_g = self.nh if self.has_gate else 0
         self.w_in = self.w_o = self.w_uk = self.w_uv = self.c_norm = self.sink = None
-        self.w_q = None                 # with U_k folded in: queries come out per head in latent coordinates
         self.fold_k = self.fold_v = False
 
     # ---- weights -------------------------------------------------------------
@@ -96,26 +96,26 @@ class LatentAttention:
         folding = self.dtype == torch.bfloat16 and w_q.dtype == torch.bfloat16 and w_o.dtype == torch.bfloat16
         self.fold_k = folding and folds(self.rank, self.dk, self.nh, self.hidden)
         self.fold_v = folding and folds(self.rank, self.dv, self.nh, self.hidden)
-        parts = [] if self.fold_k else [w_q]
         if self.fold_k:
-            # W_q'[h] = U_k[h]^T W_q[h]: [rank, qk_dim] x [qk_dim, width] per head
+            # W_q'[h] = U_k[h]^T W_q[h]: [rank, qk_dim] x [qk_dim, width] per head; the queries then
+            # come out of the input product in latent coordinates, `rank` numbers per head
             uk = tensors[n["up_k"]].double().view(self.nh, self.dk, self.rank)
             wq = w_q.double().view(self.nh, self.dk, self.hidden)
-            self.w_q = torch.einsum("hdr,hdw->hrw", uk, wq).reshape(self.nh * self.rank, self.hidden) \
+            w_q = torch.einsum("hdr,hdw->hrw", uk, wq).reshape(self.nh * self.rank, self.hidden) \
                 .to(torch.bfloat16).contiguous()
-            self.n_q = 0
+            self.n_q = self.nh * self.rank
+        parts = [w_q]
         if not self.shared_kv:
             parts.append(tensors[n["down"]])
             self.c_norm = tensors[n["down_norm"]].to(torch.float32).contiguous()
         if self.has_gate:
             parts.append(tensors[n["gate"]])
-        if parts:
-            common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
-            rows = sum(p.shape[0] for p in parts)
-            pad = -rows % 8                     # rows of the product's output start on 16 bytes
-            if pad:
-                parts.append(torch.zeros((pad, self.hidden), dtype=common, device=parts[0].device))
-            self.w_in = torch.cat([p.to(common) for p in parts], dim=0).contiguous()
+        common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
+        rows = sum(p.shape[0] for p in parts)
+        pad = -rows % 8                         # rows of the product's output start on 16 bytes
+        if pad:
+            parts.append(torch.zeros((pad, self.hidden), dtype=common, device=parts[0].device))
+        self.w_in = torch.cat([p.to(common) for p in parts], dim=0).contiguous()
         if self.fold_v:
             # W_o'[:, h] = W_o[:, h] U_v[h]: [width, v_dim] x [v_dim, rank] per head
             uv = tensors[n["up_v"]].double().view(self.nh, self.dv, self.rank)
@@ -131,12 +131,12 @@ class LatentAttention:
             self.sink = tensors[n["sink"]].to(torch.float32).contiguous()
 
     def weights(self):
-        return [t for t in (self.w_q, self.w_in, self.w_o, self.w_uk, self.w_uv, self.c_norm, self.sink)
+        return [t for t in (self.w_in, self.w_o, self.w_uk, self.w_uv, self.c_norm, self.sink)
                 if t is not None]
 
     def notices(self) -> list:
         from ..cache.storage import PAGE_SIZE
-        return (kernels.product_notices("latent attention input", self.w_in if self.w_in is not None else self.w_q, self.dtype)
+        return (kernels.product_notices("latent attention input", self.w_in, self.dtype)
                 + kernels.product_notices("latent attention output", self.w_o, self.dtype)
                 + kernels.attention_notices("latent attention", self.rank, PAGE_SIZE, self.dtype))
 
@@ -186,28 +186,25 @@ class LatentAttention:
         ws = ctx.workspace
         if view is None or view.planes != 1:
             raise kernels.KernelError("latent_attention: needs latent pages (one panel per page)")
-        qa = ws.buffer("latent.q", (T, self.nh * self.rank), self.dtype)
-        if self.fold_k:
-            kernels.linear(u, self.w_q, qa)
-        q = d = gate = None
-        if self.w_in is not None:
-            proj = ws.buffer("latent.in", (T, self.w_in.shape[0]), self.dtype)
-            kernels.linear(u, self.w_in, proj)
-            q = proj[:, :self.n_q]
-            d = proj[:, self.n_q:self.n_q + self.n_c] if self.n_c else None
-            gate = proj[:, self.n_q + self.n_c:self.n_q + self.n_c + self.n_g] if self.n_g else None
+        proj = ws.buffer("latent.in", (T, self.w_in.shape[0]), self.dtype)
+        kernels.linear(u, self.w_in, proj)
+        q = proj[:, :self.n_q]
+        d = proj[:, self.n_q:self.n_q + self.n_c] if self.n_c else None
+        gate = proj[:, self.n_q + self.n_c:self.n_q + self.n_c + self.n_g] if self.n_g else None
         rows, ring, taps = keep if keep is not None else (None, None, 0)
         if d is not None or ring is not None:
             kernels.latent_keep(d, self.c_norm, self.eps, view.pages if d is not None else None,
                                 rows, ring, taps, ctx)
-        if not self.fold_k:
+        if self.fold_k:
+            qa = q                          # columns of the product's output: the attention reads them in place
+        else:
+            qa = ws.buffer("latent.q", (T, self.nh * self.rank), self.dtype)
             self._per_head(q, self.w_uk, qa, False, None)
         mix = ws.buffer("latent.mix", (T, self.nh * self.rank), self.dtype)
+        # with U_v folded into the output matrix the heads' gate is the attention's last step
         kernels.attention(qa, mix, view.pages, ctx, self.nh, 1, self.rank, view.page_size, 0, self.scale,
-                          sink=self.sink, planes=1)
+                          sink=self.sink, planes=1, gate=gate if self.fold_v else None)
         if self.fold_v:
-            if gate is not None:
-                kernels.head_gate(mix, gate, self.nh)
             o = mix
         else:
             o = ws.buffer("latent.o", (T, self.nh * self.dv), self.dtype)

@@ -157,7 +157,7 @@ def test_products_per_head(T, heads, n, r):
     assert np.abs(out4.float().cpu().numpy() - ref4.reshape(T, -1)).max() <= 0.005 * np.abs(ref4).max() + 1e-3
 
 
-def _latent_attention_case(rank, heads, length, hot, dtype, decode):
+def _latent_attention_case(rank, heads, length, hot, dtype, decode, wide=False):
     """Latents on scattered pages; every query is made to point at the latent of position ``hot``
     with a score that towers over the rest, so a key that is dropped, doubled or read from the
     wrong row changes the result by orders of magnitude more than rounding does."""
@@ -190,7 +190,16 @@ def _latent_attention_case(rank, heads, length, hot, dtype, decode):
     ctx.kv_len_hint = 0
     qd = dev(q[rows].reshape(len(rows), -1), td)
     out = torch.empty_like(qd)
-    kernels.attention(qd, out, pages, ctx, heads, 1, rank, 64, 0, scale, sink=dev(sink), planes=1)
+    gate = None
+    if wide:
+        # as a mixer hands them over: queries and gates as column ranges of one wider buffer
+        g = to_bf16_values(rng.standard_normal((length, heads)) * 2)
+        both = torch.full((len(rows), heads * rank + heads + 6), 7.0, dtype=td, device=DEV)
+        both[:, :heads * rank] = qd
+        both[:, heads * rank:heads * rank + heads] = dev(g[rows], td)
+        qd, gate = both[:, :heads * rank], both[:, heads * rank:heads * rank + heads]
+        ref = ref * SP.sigmoid(g.astype(np.float64))[:, :, None]
+    kernels.attention(qd, out, pages, ctx, heads, 1, rank, 64, 0, scale, sink=dev(sink), planes=1, gate=gate)
     torch.cuda.synchronize()
     err = np.abs(out.float().cpu().numpy().reshape(len(rows), heads, rank) - ref[rows]).max()
     assert err < (2e-5 if dtype == "float32" else 0.02), (err, rank, length, hot)
@@ -204,6 +213,9 @@ def test_attention_over_latents_finds_a_far_key(rank, heads, dtype):
                         (700, 255), (700, 256), (700, 511), (700, 512), (513, 512), (1, 0), (2, 0)]:
         _latent_attention_case(rank, heads, length, hot, dtype, decode=False)
         _latent_attention_case(rank, heads, length, hot, dtype, decode=True)
+    for length, hot in [(321, 128), (200, 0), (700, 512)]:       # queries with a row stride, and the heads' gate
+        _latent_attention_case(rank, heads, length, hot, dtype, decode=False, wide=True)
+        _latent_attention_case(rank, heads, length, hot, dtype, decode=True, wide=True)
 
 
 # ----------------------------------------------------------------------------
@@ -308,7 +320,8 @@ def test_up_projections_folded_where_the_rank_allows(engines):
     from gguf2bin_b200.parts.latent import folds
     mixers = [b.mixer for b in engines("t", "bfloat16").model.blocks]
     assert [(m.fold_k, m.fold_v) for m in mixers] == [(True, True), (True, True), (True, True)]
-    assert mixers[2].w_uk is None and mixers[2].w_uv is None and mixers[1].w_in is not None
+    assert mixers[2].w_uk is None and mixers[2].w_uv is None
+    assert mixers[1].w_in.shape[0] == -(-(2 * 64 + 2) // 8) * 8        # queries in latent coordinates, then the gates
     assert not any(b.mixer.fold_k or b.mixer.fold_v for b in engines("t", "float32").model.blocks)
     # rank 64 over heads of 8 numbers: never folded; over heads of 40: folded while the model is small
     q = [b.mixer for b in engines("q", "bfloat16").model.blocks]

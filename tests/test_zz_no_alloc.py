@@ -37,7 +37,7 @@ def _library():
                                             ctypes.c_float, ci, vp]
     lib.g2b_attn_decode.restype = ci
     lib.g2b_attn_decode.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci,
-                                    ctypes.c_float, ci, vp, vp, vp, ci, vp]
+                                    ctypes.c_float, ci, vp, vp, vp, ci, ci, vp, ci, vp]
     lib.g2b_last_error.restype = ctypes.c_char_p
     lib.g2b_attn_decode_noalloc_scratch_bytes.restype = ctypes.c_ulonglong
     lib.g2b_attn_decode_chunk_keys.restype = ci
@@ -104,7 +104,7 @@ def test_two_calls_in_a_row_match_the_plain_attention_and_the_ordinary_entry_poi
         part_ml = torch.empty(len(lens) * nh * n_chunks * 2, dtype=torch.float32, device=DEV)
         same = torch.empty_like(q)
         rc = lib.g2b_attn_decode(*_args(q, same, cache, table, pos, seq, nh, nkv, window),
-                                 part_o.data_ptr(), part_ml.data_ptr(), None, 2, stream)
+                                 part_o.data_ptr(), part_ml.data_ptr(), None, 2, nh * HD, None, 0, stream)
         assert rc == 0, lib.g2b_last_error().decode()
         torch.cuda.synchronize()
         free_before = torch.cuda.mem_get_info()[0]
