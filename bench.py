@@ -265,7 +265,7 @@ def senotar_config(width, heads, dim, rank, ff, layers, vocab) -> dict:
             mixer["kv_from"] = i - 1
         out.append(dict(type="latent_attention", mixer=mixer, mlp=dict(kind="dense", ff=ff)))
     return dict(architecture="Senotar", width=width, vocab=vocab, norm=dict(eps=1e-6), canon=dict(taps=3),
-                embedding=dict(scale=float(width) ** 0.5, bigram=dict(buckets=100003, mul_prev=127, mul_cur=7)),
+                embedding=dict(scale=float(width) ** 0.5, bigram=dict(buckets=100003, mul_prev=131, mul_cur=5)),
                 layers=out)
 
 

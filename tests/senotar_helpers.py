@@ -35,10 +35,11 @@ CONFIGS = {
     "q": _config(96, 257, 2, 97, 1, 1, 1.0, 1e-5,
                  [_layer(1, 32, 16, 64, 128, scale=0.3), _layer(3, 8, 40, 64, 64, kv_from=0),
                   _layer(2, 24, 24, 32, 200), _layer(5, 8, 8, 64, 56, kv_from=0)]),
-    # rank 64 and 128: the sizes the tensor-core attention kernels take; four taps
+    # rank 64 and 128, the sizes the tensor-core attention kernels take, over heads so small that the
+    # up-projections stay products of their own; four taps
     "r": _config(128, 500, 4, 1000, 7, 3, 11.3, 1e-6,
-                 [_layer(4, 32, 32, 64, 256), _layer(4, 32, 32, 64, 256, kv_from=0),
-                  _layer(2, 64, 64, 128, 192)]),
+                 [_layer(6, 8, 8, 64, 320), _layer(4, 12, 8, 64, 192, kv_from=0),
+                  _layer(2, 16, 16, 128, 192)]),
     # ranks at or below the head sizes: bfloat16 multiplies the up-projections into the query and output
     # matrices (both in layers 0 and 1, the keys' only in layer 2)
     "t": _config(128, 200, 3, 64, 5, 9, 4.0, 1e-6,

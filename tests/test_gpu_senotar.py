@@ -52,7 +52,7 @@ def test_pair_embedding_over_steps(cuts):
     """Two sequences in every step, cut alike; the previous token crosses the steps in the ring."""
     from gguf2bin_b200 import kernels
     rng = np.random.default_rng(0)
-    V, H, buckets, mp, mc = 50, 40, 13, 127, 7
+    V, H, buckets, mp, mc = 50, 40, 13, 113, 11
     table, pairs = to_bf16_values(rng.standard_normal((V, H))), to_bf16_values(rng.standard_normal((buckets + 1, H)))
     w = 1 + 0.1 * rng.standard_normal(H).astype(np.float32)
     seqs = [rng.integers(0, V, 9).tolist(), rng.integers(0, V, 9).tolist()]
@@ -326,6 +326,7 @@ def test_up_projections_folded_where_the_rank_allows(engines):
     # rank 64 over heads of 8 numbers: never folded; over heads of 40: folded while the model is small
     q = [b.mixer for b in engines("q", "bfloat16").model.blocks]
     assert (q[1].fold_k, q[1].fold_v) == (False, True) and (q[3].fold_k, q[3].fold_v) == (False, False)
+    assert not any(b.mixer.fold_k or b.mixer.fold_v for b in engines("r", "bfloat16").model.blocks)
     assert folds(128, 128, 32, 4096) and folds(192, 128, 32, 4096) and not folds(512, 128, 32, 4096)
     assert folds(128, 64, 16, 1024) and not folds(512, 64, 16, 1024) and not folds(256, 128, 32, 4096)
 
