@@ -6,7 +6,8 @@
 // Formula (src/l5_model.c:518, 559-577 of AnonymoDGH/gguf2bin): kv head = head / group;
 // s_t = (q . K_t) * scale for t <= pos (the loop bound is the causal mask); softmax with
 // the maximum subtracted (src/l3_math.c:52-56); o = sum_t p_t V_t.  `window` > 0 keeps
-// only the keys with pos - window < t <= pos.
+// only the keys with pos - window < t <= pos; `chunk` > 0 keeps only the keys of the token's own
+// chunk, floor(pos / chunk) * chunk <= t <= pos (chunks count from position 0 of the sequence).
 //
 // Keys are visited in chunks of 32 that start at absolute positions that are multiples
 // of 32, with a running maximum and sum, so the arithmetic for a (token, head) depends
@@ -33,7 +34,7 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
                     const int *__restrict__ page_table, int P, int n_tokens, int nh, int nkv,
                     int hd, int page_size, int window, float scale,
                     const float *__restrict__ sink, int planes, int q_stride,
-                    const T *__restrict__ gate, int gate_stride) {
+                    const T *__restrict__ gate, int gate_stride, int chunk) {
   pdl_launch();
   pdl_wait();
   __shared__ float qs[AG_WARPS][AG_MAX_HD];
@@ -43,7 +44,7 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
   const int t = (int)(item / nh), h = (int)(item % nh);
   const int pos = tok_pos[t], b = tok_seq[t];
   const int kvh = h / (nh / nkv);
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = chunk > 0 ? (pos / chunk) * chunk : (window > 0 ? max(0, pos - window + 1) : 0);
 
   const T *qp = q + (size_t)t * q_stride + (size_t)h * hd;
   for (int j = lane; j < hd; j += 32) qs[warp][j] = to_f32(qp[j]);
@@ -103,8 +104,9 @@ extern "C" int g2b_attn_generic(const void *q, void *out, int dtype, const void 
                                 const int *tok_pos, const int *tok_seq, const int *page_table,
                                 int P, int n_tokens, int nh, int nkv, int hd, int page_size,
                                 int window, float scale, const float *sink, int planes, int q_stride,
-                                const void *gate, int gate_stride, cudaStream_t stream) {
+                                const void *gate, int gate_stride, int chunk, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (chunk < 0 || (chunk > 0 && window > 0)) G2B_REFUSE("attn_generic: a chunk of %d keys with a window of %d", chunk, window);
   if (planes != 1 && planes != 2) G2B_REFUSE("attn_generic: %d panels per page and kv head (1 or 2)", planes);
   if (hd <= 0 || hd > AG_MAX_HD) G2B_REFUSE("attn_generic: head_dim %d outside 1..%d", hd, AG_MAX_HD);
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_generic: %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -115,11 +117,11 @@ extern "C" int g2b_attn_generic(const void *q, void *out, int dtype, const void 
   if (dtype == G2B_F32)
     g2b_launch(attn_generic_kernel<float>, dim3(blocks), dim3(AG_WARPS * 32), 0, stream, 
         (const float *)q, (float *)out, (const float *)cache, tok_pos, tok_seq, page_table, P,
-        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes, q_stride, (const float *)gate, gate_stride);
+        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes, q_stride, (const float *)gate, gate_stride, chunk);
   else if (dtype == G2B_BF16)
     g2b_launch(attn_generic_kernel<bf16>, dim3(blocks), dim3(AG_WARPS * 32), 0, stream, 
         (const bf16 *)q, (bf16 *)out, (const bf16 *)cache, tok_pos, tok_seq, page_table, P,
-        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes, q_stride, (const bf16 *)gate, gate_stride);
+        n_tokens, nh, nkv, hd, page_size, window, scale, sink, planes, q_stride, (const bf16 *)gate, gate_stride, chunk);
   else
     G2B_REFUSE("attn_generic: unknown dtype %d", dtype);
   return g2b_check_launch("attn_generic");

@@ -1,0 +1,397 @@
+// A routed feed-forward: every token goes through `top` of a layer's small feed-forwards.
+//
+//   moe_route    scores s = softmax(z) over all experts in 32-bit; the `top` largest of s + c
+//                (c: a stored correction that steers the choice only) are chosen, ties to the
+//                lower index; the weights are the chosen experts' s as they are, or divided by
+//                their sum.  idx [T, top], weight [T, top].
+//   moe_plan     the step's (token, choice) pairs grouped by expert: how many rows every expert
+//                gets, where its rows start, which pair sits in which row, and the list of row
+//                tiles that the products walk.  Experts from `n_real` on have no matrices (their
+//                output is their input); their pairs get no row.
+//   moe_gemm     one product per expert over its rows: out = A_rows . W_e^T, the rows of A
+//                gathered by the plan; with `swiglu` W_e holds gate rows then up rows and the
+//                output is silu(gate) * up.  32-bit accumulation; a row's sum runs over k in
+//                ascending order whatever else is in the tile.
+//   moe_combine  y_t = sum_j weight_tj * (row of pair (t, j), or the token's own input for an
+//                expert without matrices), added in the order of j.
+//
+// Which row of an expert's range a pair lands in depends on the batch (the plan hands rows out
+// with atomic counters); what is computed for the pair does not: a row of a product depends on
+// that row alone, and the combination adds a token's choices in the order of the choice.
+#include "common.cuh"
+#include "mma.cuh"
+
+G2B_DEFINE_LAST_ERROR
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+
+// ---------------------------------------------------------------------------
+// router
+// ---------------------------------------------------------------------------
+#define ROUTE_WARPS 4
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const float *__restrict__ z, const float *__restrict__ correction, int T, int N, int top,
+                 int renormalise, int *__restrict__ idx, float *__restrict__ weight) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float sm[];                 // per warp: s [N], pick [N]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= T) return;
+  float *s = sm + (size_t)warp * 2 * N, *pick = s + N;
+  const float *zr = z + (size_t)t * N;
+  float m = -INFINITY;
+  for (int j = lane; j < N; j += 32) m = fmaxf(m, zr[j]);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int j = lane; j < N; j += 32) {
+    const float e = expf(zr[j] - m);
+    s[j] = e;
+    sum += e;
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int j = lane; j < N; j += 32) {
+    s[j] *= inv;
+    pick[j] = s[j] + (correction ? correction[j] : 0.f);
+  }
+  __syncwarp();
+  float chosen_sum = 0.f;
+  for (int r = 0; r < top; ++r) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int j = lane; j < N; j += 32)
+      if (pick[j] > best) { best = pick[j]; at = j; }
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, off);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at >= N) at = 0;                        // all NaN: never read outside
+    if (lane == 0) {
+      idx[(size_t)t * top + r] = at;
+      weight[(size_t)t * top + r] = s[at];
+      pick[at] = -INFINITY;
+    }
+    chosen_sum += s[at];
+    __syncwarp();
+  }
+  if (renormalise && lane == 0)
+    for (int r = 0; r < top; ++r) weight[(size_t)t * top + r] /= chosen_sum;
+}
+
+extern "C" int g2b_moe_route(const float *z, const float *correction, int T, int N, int top, int renormalise,
+                             int *idx, float *weight, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (top < 1 || top > N) G2B_REFUSE("moe_route: %d choices among %d experts", top, N);
+  const size_t smem = (size_t)ROUTE_WARPS * 2 * N * sizeof(float);
+  if (smem > 48 * 1024) G2B_REFUSE("moe_route: %d experts are more than a block's shared memory holds", N);
+  g2b_launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, z,
+             correction, T, N, top, renormalise, idx, weight);
+  return g2b_check_launch("moe_route");
+}
+
+// ---------------------------------------------------------------------------
+// plan: one block
+// ---------------------------------------------------------------------------
+#define PLAN_MAX_EXPERTS 1024
+// plan layout (int32): [0] tiles in use, [1..E+1] first row of each expert (and the end),
+// then the tiles as (expert, first row, rows) triples from word PLAN_TILES_AT(E) on
+#define PLAN_TILES_AT(E) ((E) + 2)
+
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int *__restrict__ idx, int n_pairs, int n_real, int tile_rows, int max_tiles,
+                int *__restrict__ plan, int *__restrict__ row_pair, int *__restrict__ pair_row) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ int count[PLAN_MAX_EXPERTS], start[PLAN_MAX_EXPERTS + 1], cursor[PLAN_MAX_EXPERTS];
+  for (int e = threadIdx.x; e < n_real; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = idx[p];
+    if (e >= 0 && e < n_real) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    int *tl = plan + PLAN_TILES_AT(n_real);
+    for (int e = 0; e < n_real; ++e) {
+      start[e] = at;
+      plan[1 + e] = at;
+      for (int r = 0; r < count[e] && tiles < max_tiles; r += tile_rows, ++tiles) {
+        tl[3 * tiles + 0] = e;
+        tl[3 * tiles + 1] = at + r;
+        tl[3 * tiles + 2] = min(tile_rows, count[e] - r);
+      }
+      at += count[e];
+    }
+    start[n_real] = at;
+    plan[1 + n_real] = at;
+    plan[0] = tiles;
+  }
+  for (int e = threadIdx.x; e < n_real; e += blockDim.x) cursor[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = idx[p];
+    int row = -1;
+    if (e >= 0 && e < n_real) {
+      row = start[e] + atomicAdd(&cursor[e], 1);
+      row_pair[row] = p;
+    }
+    pair_row[p] = row;
+  }
+}
+
+extern "C" int g2b_moe_plan(const int *idx, int n_pairs, int n_real, int tile_rows, int max_tiles, int *plan,
+                            int *row_pair, int *pair_row, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (n_real < 0 || n_real > PLAN_MAX_EXPERTS) G2B_REFUSE("moe_plan: %d experts outside 0..%d", n_real, PLAN_MAX_EXPERTS);
+  g2b_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, idx, n_pairs, n_real, tile_rows, max_tiles, plan, row_pair,
+             pair_row);
+  return g2b_check_launch("moe_plan");
+}
+
+// ---------------------------------------------------------------------------
+// one product per expert over its rows (CUDA cores, any type)
+// ---------------------------------------------------------------------------
+#define MG_BM 32
+#define MG_BN 64
+#define MG_BK 16
+// 128 threads: thread (ty, tx) = (i / 16, i % 16) owns rows ty*4..+3 and columns tx + 16*j, j < 4
+
+template <typename T, bool SWIGLU>
+__global__ void __launch_bounds__(128)
+moe_gemm_kernel(const T *__restrict__ A, int a_stride, const int *__restrict__ row_pair, int pairs_per_token,
+                const T *__restrict__ W, int N, int K, const int *__restrict__ plan, int n_real,
+                void *__restrict__ out, int out_f32) {
+  pdl_launch();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int *tl = plan + PLAN_TILES_AT(n_real) + 3 * tile;
+  const int e = tl[0], row0 = tl[1], rows = tl[2];
+  const int n0 = blockIdx.x * MG_BN;
+  __shared__ float As[MG_BK][MG_BM + 1];
+  __shared__ float Bs[SWIGLU ? 2 : 1][MG_BK][MG_BN + 1];
+  __shared__ int src_row[MG_BM];
+  const int tid = threadIdx.x;
+  if (tid < MG_BM) {
+    int r = -1;
+    if (tid < rows) r = row_pair ? row_pair[row0 + tid] / pairs_per_token : row0 + tid;
+    src_row[tid] = r;
+  }
+  __syncthreads();
+  const int ty = tid / 16, tx = tid % 16;
+  const size_t w_rows = SWIGLU ? 2 * (size_t)N : (size_t)N;
+  const T *We = W + (size_t)e * w_rows * K;
+  float acc[SWIGLU ? 2 : 1][4][4];
+#pragma unroll
+  for (int s = 0; s < (SWIGLU ? 2 : 1); ++s)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[s][i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += MG_BK) {
+    for (int i = tid; i < MG_BM * MG_BK; i += 128) {
+      const int r = i / MG_BK, kk = i % MG_BK;
+      const int sr = src_row[r];
+      As[kk][r] = (sr >= 0 && k0 + kk < K) ? to_f32(A[(size_t)sr * a_stride + k0 + kk]) : 0.f;
+    }
+    for (int i = tid; i < MG_BN * MG_BK; i += 128) {
+      const int c = i / MG_BK, kk = i % MG_BK;
+      const bool in = n0 + c < N && k0 + kk < K;
+      Bs[0][kk][c] = in ? to_f32(We[(size_t)(n0 + c) * K + k0 + kk]) : 0.f;
+      if (SWIGLU) Bs[1][kk][c] = in ? to_f32(We[((size_t)N + n0 + c) * K + k0 + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MG_BK; ++kk) {
+      float av[4], bv[SWIGLU ? 2 : 1][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int s = 0; s < (SWIGLU ? 2 : 1); ++s)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bv[s][j] = Bs[s][kk][tx + 16 * j];
+#pragma unroll
+      for (int s = 0; s < (SWIGLU ? 2 : 1); ++s)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[s][i][j] = fmaf(av[i], bv[s][j], acc[s][i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = n0 + tx + 16 * j;
+      if (c >= N) continue;
+      const float v = SWIGLU ? silu_f(acc[0][i][j]) * acc[SWIGLU ? 1 : 0][i][j] : acc[0][i][j];
+      const size_t at = (size_t)(row0 + r) * N + c;
+      if (out_f32) ((float *)out)[at] = v;
+      else ((T *)out)[at] = from_f32<T>(v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// the same on the tensor cores (bfloat16, mma.sync m16n8k16): a tile of 32 rows x 64 columns,
+// four warps side by side, each 32 x 16
+// ---------------------------------------------------------------------------
+#define MT_BK 32
+#define MT_PAD 8
+template <bool SWIGLU>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const bf16 *__restrict__ A, int a_stride, const int *__restrict__ row_pair, int pairs_per_token,
+                    const bf16 *__restrict__ W, int N, int K, const int *__restrict__ plan, int n_real,
+                    void *__restrict__ out, int out_f32) {
+  pdl_launch();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int *tl = plan + PLAN_TILES_AT(n_real) + 3 * tile;
+  const int e = tl[0], row0 = tl[1], rows = tl[2];
+  const int n0 = blockIdx.x * MG_BN;
+  constexpr int S = SWIGLU ? 2 : 1;
+  __shared__ __align__(16) bf16 As[MG_BM][MT_BK + MT_PAD];
+  __shared__ __align__(16) bf16 Bs[S][MG_BN][MT_BK + MT_PAD];
+  __shared__ int src_row[MG_BM];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < MG_BM) {
+    int r = -1;
+    if (tid < rows) r = row_pair ? row_pair[row0 + tid] / pairs_per_token : row0 + tid;
+    src_row[tid] = r;
+  }
+  __syncthreads();
+  const bf16 *We = W + (size_t)e * (size_t)S * N * K;
+  float acc[S][2][2][4];                        // [gate|up][16-row block][8-column block][fragment]
+#pragma unroll
+  for (int s = 0; s < S; ++s)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int f = 0; f < 4; ++f) acc[s][i][j][f] = 0.f;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int k0 = 0; k0 < K; k0 += MT_BK) {       // K is a multiple of 8: 16-byte pieces
+    for (int i = tid; i < MG_BM * (MT_BK / 8); i += 128) {
+      const int r = i / (MT_BK / 8), p = i % (MT_BK / 8);
+      const int sr = src_row[r];
+      uint4 v = zero;
+      if (sr >= 0 && k0 + p * 8 < K) v = *(const uint4 *)(A + (size_t)sr * a_stride + k0 + p * 8);
+      *(uint4 *)&As[r][p * 8] = v;
+    }
+    for (int i = tid; i < S * MG_BN * (MT_BK / 8); i += 128) {
+      const int s = i / (MG_BN * (MT_BK / 8)), c = (i / (MT_BK / 8)) % MG_BN, p = i % (MT_BK / 8);
+      uint4 v = zero;
+      if (n0 + c < N && k0 + p * 8 < K) v = *(const uint4 *)(We + ((size_t)s * N + n0 + c) * K + k0 + p * 8);
+      *(uint4 *)&Bs[s][c][p * 8] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MT_BK; kk += 16) {
+      const int g = lane >> 2, q = lane & 3;
+      uint32_t a[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        a[i][0] = *(const uint32_t *)&As[16 * i + g][kk + 2 * q];
+        a[i][1] = *(const uint32_t *)&As[16 * i + g + 8][kk + 2 * q];
+        a[i][2] = *(const uint32_t *)&As[16 * i + g][kk + 2 * q + 8];
+        a[i][3] = *(const uint32_t *)&As[16 * i + g + 8][kk + 2 * q + 8];
+      }
+#pragma unroll
+      for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int c = warp * 16 + 8 * j + g;
+          uint32_t b[2];
+          b[0] = *(const uint32_t *)&Bs[s][c][kk + 2 * q];
+          b[1] = *(const uint32_t *)&Bs[s][c][kk + 2 * q + 8];
+#pragma unroll
+          for (int i = 0; i < 2; ++i) mma_bf16_16816(acc[s][i][j], a[i], b[0], b[1]);
+        }
+    }
+    __syncthreads();
+  }
+  const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        const int r = 16 * i + g + (f >> 1) * 8;
+        const int c = n0 + warp * 16 + 8 * j + 2 * q + (f & 1);
+        if (r >= rows || c >= N) continue;
+        const float v = SWIGLU ? silu_f(acc[0][i][j][f]) * acc[S - 1][i][j][f] : acc[0][i][j][f];
+        const size_t at = (size_t)(row0 + r) * N + c;
+        if (out_f32) ((float *)out)[at] = v;
+        else ((bf16 *)out)[at] = __float2bfloat16_rn(v);
+      }
+}
+
+extern "C" int g2b_moe_tile_rows() { return MG_BM; }
+
+extern "C" int g2b_moe_gemm(const void *A, int dtype, int a_stride, const int *row_pair, int pairs_per_token,
+                            const void *W, int N, int K, const int *plan, int n_real, int max_tiles, int swiglu,
+                            void *out, int out_f32, cudaStream_t stream) {
+  if (max_tiles <= 0 || N <= 0) return 0;
+  const dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
+  if (dtype == G2B_F32) {
+    if (swiglu)
+      g2b_launch(moe_gemm_kernel<float, true>, grid, dim3(128), 0, stream, (const float *)A, a_stride, row_pair,
+                 pairs_per_token, (const float *)W, N, K, plan, n_real, out, out_f32);
+    else
+      g2b_launch(moe_gemm_kernel<float, false>, grid, dim3(128), 0, stream, (const float *)A, a_stride, row_pair,
+                 pairs_per_token, (const float *)W, N, K, plan, n_real, out, out_f32);
+  } else if (dtype == G2B_BF16) {
+    const bool mma = K % 8 == 0 && a_stride % 8 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0;
+    if (mma && swiglu)
+      g2b_launch(moe_gemm_mma_kernel<true>, grid, dim3(128), 0, stream, (const bf16 *)A, a_stride, row_pair,
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+    else if (mma)
+      g2b_launch(moe_gemm_mma_kernel<false>, grid, dim3(128), 0, stream, (const bf16 *)A, a_stride, row_pair,
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+    else if (swiglu)
+      g2b_launch(moe_gemm_kernel<bf16, true>, grid, dim3(128), 0, stream, (const bf16 *)A, a_stride, row_pair,
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+    else
+      g2b_launch(moe_gemm_kernel<bf16, false>, grid, dim3(128), 0, stream, (const bf16 *)A, a_stride, row_pair,
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+  } else {
+    G2B_REFUSE("moe_gemm: unknown dtype %d", dtype);
+  }
+  return g2b_check_launch("moe_gemm");
+}
+
+// ---------------------------------------------------------------------------
+// combination
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float *__restrict__ rows, const int *__restrict__ pair_row, const float *__restrict__ weight,
+                   const float *__restrict__ x_self, int T, int top, int Hw, float *__restrict__ out) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int j = threadIdx.x; j < Hw; j += blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < top; ++r) {
+      const int row = pair_row[(size_t)t * top + r];
+      const float v = row >= 0 ? rows[(size_t)row * Hw + j] : x_self[(size_t)t * Hw + j];
+      acc = fmaf(weight[(size_t)t * top + r], v, acc);
+    }
+    out[(size_t)t * Hw + j] = acc;
+  }
+}
+
+extern "C" int g2b_moe_combine(const float *rows, const int *pair_row, const float *weight, const float *x_self, int T,
+                               int top, int Hw, float *out, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  g2b_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, rows, pair_row, weight, x_self, T, top, Hw, out);
+  return g2b_check_launch("moe_combine");
+}

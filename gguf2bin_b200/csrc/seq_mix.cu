@@ -1,0 +1,554 @@
+// Kernels of mixers that carry a matrix state per head instead of keys (linear attention with a
+// decay, the gated delta rule), of the short causal convolution in front of them, and of an
+// attention prologue whose norm spans the whole projection.  All arithmetic is 32-bit;
+// activations are read and written in the compute type (float or bfloat16); states are float.
+//
+//   proj_norm_rope_cache  q, k, v of one product (+ bias); RMS norm of ALL of q (and of all of k)
+//                         at once, times a weight; rotation of the first `rot` entries of every
+//                         head, pairs (i, i + rot/2) or (2i, 2i + 1); q out, k and v into the
+//                         layer's pages.  Key and value heads may differ in size: both are
+//                         stored zero-filled to the larger, and so is q.
+//   rotate_heads          the rotation alone, in place, then times a constant
+//   short_conv            y_t = act(sum_j w[j, c] x_{t - taps + 1 + j}[c]); rows before the step's
+//                         first come from a ring of `taps` rows per slot indexed by position mod
+//                         taps; rows before position 0 are zero
+//   conv_keep             the last taps - 1 input rows of every sequence of the step into its ring
+//   state_scan            per head a state S [D, V], a token at a time:
+//                           decay:  S = a S + k v^T;                     o = S^T q
+//                           delta:  S = g S; u = b (v - S^T k); S += k u^T; o = S^T q
+//                         with a fixed per head, or g = exp(-exp(A) softplus(x + dt)) and
+//                         b = sigmoid(y) per token and head.  q and k are prepared while they are
+//                         staged: rotated (then k times a constant), or made unit vectors.
+//   head_norm_gate        o / sqrt(mean(o^2) + eps) per head (times a weight), times silu(gate)
+//   gate_mul              o * sigmoid(gate) element by element, heads unpadded
+//   norm_add              x += y / sqrt(mean(y^2) + eps) * w, and the sum again in the compute type
+//
+// A state column (all D entries that feed one output channel) never mixes with another, so a
+// block owns a range of columns of one head of one sequence and walks the step's tokens in
+// order: what it computes for a token depends on the tokens before it in the sequence only,
+// not on how they were cut into steps or on the batch.
+#include "common.cuh"
+
+G2B_DEFINE_LAST_ERROR
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// Rotation of x[0..rot) in shared memory by one warp: pairs (i, i + rot/2), or (2i, 2i + 1).
+__device__ __forceinline__ void rotate_in_place(float *x, const float2 *cs, int rot, int interleaved, int lane) {
+  const int half = rot >> 1;
+  for (int i = lane; i < half; i += 32) {
+    const float2 r = cs[i];
+    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+    const float u = x[a], v = x[b];
+    x[a] = u * r.x - v * r.y;
+    x[b] = v * r.x + u * r.y;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// attention prologue with a norm over the whole projection
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+proj_norm_rope_cache_kernel(const T *__restrict__ qkv, int row_stride, const float *__restrict__ bias,
+                            int nh, int nkv, int D, int V, const float *__restrict__ q_w,
+                            const float *__restrict__ k_w, float eps, const float2 *__restrict__ rope,
+                            int rot, int interleaved, const int *__restrict__ tok_pos,
+                            const int *__restrict__ tok_seq, const int *__restrict__ page_table, int P,
+                            T *__restrict__ cache, int page_size, T *__restrict__ q_out) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float sm[];                     // q [nh*D], k [nkv*D]
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int nq = nh * D, nk = nkv * D;
+  const int hd = D > V ? D : V;
+  const T *src = qkv + (size_t)t * row_stride;
+  float *xq = sm, *xk = sm + nq;
+  float sq = 0.f, sk = 0.f;
+  for (int j = threadIdx.x; j < nq + nk; j += blockDim.x) {
+    const float v = to_f32(src[j]) + (bias ? bias[j] : 0.f);
+    sm[j] = v;
+    if (j < nq) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
+  }
+  if (q_w) sq = block_sum(sq, scratch);
+  if (k_w) sk = block_sum(sk, scratch);
+  __syncthreads();
+  if (q_w) {
+    const float inv = 1.f / sqrtf(sq / (float)nq + eps);
+    for (int j = threadIdx.x; j < nq; j += blockDim.x) xq[j] = xq[j] * inv * q_w[j];
+  }
+  if (k_w) {
+    const float inv = 1.f / sqrtf(sk / (float)nk + eps);
+    for (int j = threadIdx.x; j < nk; j += blockDim.x) xk[j] = xk[j] * inv * k_w[j];
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  if (rope) {
+    const float2 *cs = rope + (size_t)t * (rot >> 1);
+    for (int h = warp; h < nh + nkv; h += n_warps) rotate_in_place(sm + (size_t)h * D, cs, rot, interleaved, lane);
+    __syncthreads();
+  }
+  const int pos = tok_pos[t];
+  const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
+  const int in_page = pos % page_size;
+  for (int j = threadIdx.x; j < nh * hd; j += blockDim.x) {
+    const int h = j / hd, d = j % hd;
+    q_out[(size_t)t * nh * hd + j] = from_f32<T>(d < D ? xq[h * D + d] : 0.f);
+  }
+  for (int j = threadIdx.x; j < nkv * hd; j += blockDim.x) {
+    const int h = j / hd, d = j % hd;
+    T *kd = cache + ((((size_t)page * 2 + 0) * nkv + h) * page_size + in_page) * hd;
+    T *vd = cache + ((((size_t)page * 2 + 1) * nkv + h) * page_size + in_page) * hd;
+    kd[d] = from_f32<T>(d < D ? xk[h * D + d] : 0.f);
+    vd[d] = from_f32<T>(d < V ? to_f32(src[nq + nk + h * V + d]) + (bias ? bias[nq + nk + h * V + d] : 0.f) : 0.f);
+  }
+}
+
+extern "C" int g2b_proj_norm_rope_cache(const void *qkv, int dtype, int row_stride, int T_tokens,
+                                        const float *bias, int nh, int nkv, int D, int V, const float *q_w,
+                                        const float *k_w, float eps, const float *rope, int rot, int interleaved,
+                                        const int *tok_pos, const int *tok_seq, const int *page_table, int P,
+                                        void *cache, int page_size, void *q_out, cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (rope && (rot <= 0 || rot > D || (rot & 1))) G2B_REFUSE("proj_norm_rope_cache: %d rotated entries of a head of %d", rot, D);
+  const size_t smem = (size_t)(nh + nkv) * D * sizeof(float);
+  if (smem > 200 * 1024) G2B_REFUSE("proj_norm_rope_cache: q and k of %d entries do not fit a block's shared memory", (nh + nkv) * D);
+  if (dtype == G2B_F32) {
+    auto k = proj_norm_rope_cache_kernel<float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    g2b_launch(k, dim3(T_tokens), dim3(256), smem, stream, (const float *)qkv, row_stride, bias, nh, nkv, D, V, q_w, k_w,
+               eps, (const float2 *)rope, rot, interleaved, tok_pos, tok_seq, page_table, P, (float *)cache, page_size,
+               (float *)q_out);
+  } else if (dtype == G2B_BF16) {
+    auto k = proj_norm_rope_cache_kernel<bf16>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    g2b_launch(k, dim3(T_tokens), dim3(256), smem, stream, (const bf16 *)qkv, row_stride, bias, nh, nkv, D, V, q_w, k_w,
+               eps, (const float2 *)rope, rot, interleaved, tok_pos, tok_seq, page_table, P, (bf16 *)cache, page_size,
+               (bf16 *)q_out);
+  } else {
+    G2B_REFUSE("proj_norm_rope_cache: unknown dtype %d", dtype);
+  }
+  return g2b_check_launch("proj_norm_rope_cache");
+}
+
+// ---------------------------------------------------------------------------
+// rotation alone
+// ---------------------------------------------------------------------------
+#define ROT_MAX_D 512
+template <typename T>
+__global__ void __launch_bounds__(128)
+rotate_heads_kernel(T *__restrict__ x, int row_stride, int T_tokens, int heads, int D,
+                    const float2 *__restrict__ rope, int rot, int interleaved, float scale) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float buf[4][ROT_MAX_D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * 4 + warp;
+  if (item >= (long long)T_tokens * heads) return;
+  const int t = (int)(item / heads), h = (int)(item % heads);
+  T *p = x + (size_t)t * row_stride + (size_t)h * D;
+  for (int j = lane; j < D; j += 32) buf[warp][j] = to_f32(p[j]);
+  __syncwarp();
+  rotate_in_place(buf[warp], rope + (size_t)t * (rot >> 1), rot, interleaved, lane);
+  __syncwarp();
+  for (int j = lane; j < D; j += 32) p[j] = from_f32<T>(buf[warp][j] * scale);
+}
+
+extern "C" int g2b_rotate_heads(void *x, int dtype, int row_stride, int T_tokens, int heads, int D,
+                                const float *rope, int rot, int interleaved, float scale, cudaStream_t stream) {
+  if (T_tokens <= 0 || heads <= 0) return 0;
+  if (D <= 0 || D > ROT_MAX_D) G2B_REFUSE("rotate_heads: head size %d outside 1..%d", D, ROT_MAX_D);
+  if (!rope || rot <= 0 || rot > D || (rot & 1)) G2B_REFUSE("rotate_heads: %d rotated entries of a head of %d", rot, D);
+  const unsigned blocks = (unsigned)(((long long)T_tokens * heads + 3) / 4);
+  if (dtype == G2B_F32)
+    g2b_launch(rotate_heads_kernel<float>, dim3(blocks), dim3(128), 0, stream, (float *)x, row_stride, T_tokens, heads, D,
+               (const float2 *)rope, rot, interleaved, scale);
+  else if (dtype == G2B_BF16)
+    g2b_launch(rotate_heads_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, (bf16 *)x, row_stride, T_tokens, heads, D,
+               (const float2 *)rope, rot, interleaved, scale);
+  else
+    G2B_REFUSE("rotate_heads: unknown dtype %d", dtype);
+  return g2b_check_launch("rotate_heads");
+}
+
+// ---------------------------------------------------------------------------
+// short causal convolution over time, per channel
+// ---------------------------------------------------------------------------
+#define CONV_MAX_TAPS 16
+// seq_meta [B,4]: first row of the step, rows, tokens before the step, slot; null: one token per sequence
+template <typename T>
+__global__ void __launch_bounds__(256)
+short_conv_kernel(const T *__restrict__ x, int x_stride, const float *__restrict__ w, T *__restrict__ ring,
+                  int taps, int C, int T_tokens, const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
+                  const int *__restrict__ seq_slots, const int *__restrict__ seq_meta, int act,
+                  T *__restrict__ out, int out_stride) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int b = tok_seq[t], pos = tok_pos[t];
+  const int first_row = seq_meta ? seq_meta[4 * b + 0] : t;
+  const int past = seq_meta ? seq_meta[4 * b + 2] : pos;
+  T *my_ring = ring + (size_t)seq_slots[b] * taps * C;
+  float acc = 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int p = pos - (taps - 1) + j;
+    float v = 0.f;
+    if (p >= past) v = to_f32(x[(size_t)(first_row + (p - past)) * x_stride + c]);
+    else if (p >= 0) v = to_f32(my_ring[(size_t)(p % taps) * C + c]);
+    acc = fmaf(w[(size_t)j * C + c], v, acc);
+  }
+  if (!seq_meta && taps > 1)      // one token per sequence: nobody else touches this slot's ring in this launch,
+    my_ring[(size_t)(pos % taps) * C + c] = x[(size_t)t * x_stride + c];      // and place pos % taps is not read above
+  out[(size_t)t * out_stride + c] = from_f32<T>(act ? silu_f(acc) : acc);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_keep_kernel(const T *__restrict__ x, int x_stride, T *__restrict__ ring, int taps, int C, int n_seqs,
+                 const int *__restrict__ seq_meta) {
+  pdl_launch();
+  pdl_wait();
+  const int b = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int first_row = seq_meta[4 * b + 0], n = seq_meta[4 * b + 1], past = seq_meta[4 * b + 2];
+  T *my_ring = ring + (size_t)seq_meta[4 * b + 3] * taps * C;
+  for (int r = max(0, n - (taps - 1)); r < n; ++r)
+    my_ring[(size_t)((past + r) % taps) * C + c] = x[(size_t)(first_row + r) * x_stride + c];
+}
+
+extern "C" int g2b_short_conv(const void *x, int dtype, int x_stride, const float *w, void *ring, int taps, int C,
+                              int T_tokens, int n_seqs, const int *tok_pos, const int *tok_seq, const int *seq_slots,
+                              const int *seq_meta, int act, void *out, int out_stride, cudaStream_t stream) {
+  if (T_tokens <= 0 || C <= 0) return 0;
+  if (taps < 1 || taps > CONV_MAX_TAPS) G2B_REFUSE("short_conv: %d taps outside 1..%d", taps, CONV_MAX_TAPS);
+  if (taps > 1 && !ring) G2B_REFUSE("short_conv: no ring for the rows before the step");
+  const dim3 grid((C + 255) / 256, T_tokens), keep_grid((C + 255) / 256, n_seqs);
+  if (dtype == G2B_F32) {
+    g2b_launch(short_conv_kernel<float>, grid, dim3(256), 0, stream, (const float *)x, x_stride, w, (float *)ring, taps, C,
+               T_tokens, tok_pos, tok_seq, seq_slots, seq_meta, act, (float *)out, out_stride);
+    if (seq_meta && taps > 1)
+      g2b_launch(conv_keep_kernel<float>, keep_grid, dim3(256), 0, stream, (const float *)x, x_stride, (float *)ring, taps, C,
+                 n_seqs, seq_meta);
+  } else if (dtype == G2B_BF16) {
+    g2b_launch(short_conv_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16 *)x, x_stride, w, (bf16 *)ring, taps, C,
+               T_tokens, tok_pos, tok_seq, seq_slots, seq_meta, act, (bf16 *)out, out_stride);
+    if (seq_meta && taps > 1)
+      g2b_launch(conv_keep_kernel<bf16>, keep_grid, dim3(256), 0, stream, (const bf16 *)x, x_stride, (bf16 *)ring, taps, C,
+                 n_seqs, seq_meta);
+  } else {
+    G2B_REFUSE("short_conv: unknown dtype %d", dtype);
+  }
+  return g2b_check_launch("short_conv");
+}
+
+// ---------------------------------------------------------------------------
+// the state scan
+// ---------------------------------------------------------------------------
+// A column of the state (D entries) is held by L lanes of one warp, R = ceil(D / L) <= 16 entries
+// each: lane l holds rows r * L + l.  The state is stored column by column ([slot, head, V, D]), so
+// the L lanes of a column read L consecutive floats per r.
+#define SCAN_THREADS 256
+#define SCAN_R 16
+#define SCAN_TILE 8           // tokens staged at a time (one warp prepares one token's q and k)
+#define SCAN_MAX_D 512
+
+struct ScanArgs {
+  const void *q, *k, *v;      // compute type; rows of wider buffers
+  int q_stride, k_stride, v_stride;
+  int H, G, D, V;             // value heads, query/key heads, key size, value size
+  const float2 *rope;         // [T, rot/2] or null
+  int rot, interleaved;
+  float q_scale, k_scale;     // after rotation / after the unit norm
+  int unit_norm;              // q and k divided by sqrt(sum x^2 + unit_eps) first
+  float unit_eps;
+  const float *decay;         // mode 0: [H]
+  const float *ab;            // mode 1: [T, 2H] float: decay input x, then write-strength input y
+  const float *A_log, *dt_bias;      // mode 1: [H]
+  float *state;               // [slots, H, V, D]
+  const int *tok_pos, *seq_slots, *seq_meta;
+  float *out;                 // [T, H*V] float
+  int n_tokens;
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(SCAN_THREADS)
+state_scan_kernel(const ScanArgs a, int L) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sq[SCAN_TILE][SCAN_MAX_D];
+  __shared__ float sk[SCAN_TILE][SCAN_MAX_D];
+  __shared__ float sv[SCAN_TILE][SCAN_THREADS / 8];
+  __shared__ float sg[SCAN_TILE], sb[SCAN_TILE];
+  const int D = a.D, V = a.V, H = a.H;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qk_head = h / (H / a.G);
+  const int cols = SCAN_THREADS / L;
+  const int lane_in_col = threadIdx.x % L;
+  const int col_local = threadIdx.x / L;
+  const int c = blockIdx.x * cols + col_local;
+  const bool live = c < V;
+  const int first_row = a.seq_meta ? a.seq_meta[4 * b + 0] : b;
+  const int n = a.seq_meta ? a.seq_meta[4 * b + 1] : 1;
+  const int slot = a.seq_slots[b];
+  const int R = (D + L - 1) / L;
+  float *sp = a.state + (((size_t)slot * H + h) * V + (live ? c : 0)) * D;
+  float S[SCAN_R];
+#pragma unroll
+  for (int r = 0; r < SCAN_R; ++r) {
+    const int d = r * L + lane_in_col;
+    S[r] = (live && r < R && d < D) ? sp[d] : 0.f;
+  }
+  float decay = 1.f, A = 0.f, dt = 0.f;
+  if (MODE == 0) decay = a.decay[h];
+  else { A = expf(a.A_log[h]); dt = a.dt_bias[h]; }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T *qg = (const T *)a.q, *kg = (const T *)a.k, *vg = (const T *)a.v;
+
+  for (int t0 = 0; t0 < n; t0 += SCAN_TILE) {
+    const int nt = min(SCAN_TILE, n - t0);
+    __syncthreads();                              // the tile before is used up
+    if (warp < nt) {                              // SCAN_TILE == warps of the block: one token each
+      const int row = first_row + t0 + warp;
+      const T *qp = qg + (size_t)row * a.q_stride + (size_t)qk_head * D;
+      const T *kp = kg + (size_t)row * a.k_stride + (size_t)qk_head * D;
+      float nq = 0.f, nk = 0.f;
+      for (int j = lane; j < D; j += 32) {
+        const float x = to_f32(qp[j]), y = to_f32(kp[j]);
+        sq[warp][j] = x;
+        sk[warp][j] = y;
+        nq = fmaf(x, x, nq);
+        nk = fmaf(y, y, nk);
+      }
+      __syncwarp();
+      float fq = a.q_scale, fk = a.k_scale;
+      if (a.unit_norm) {
+        fq *= 1.f / sqrtf(warp_sum(nq) + a.unit_eps);
+        fk *= 1.f / sqrtf(warp_sum(nk) + a.unit_eps);
+      }
+      if (a.rope) {
+        const float2 *cs = a.rope + (size_t)row * (a.rot >> 1);
+        rotate_in_place(sq[warp], cs, a.rot, a.interleaved, lane);
+        rotate_in_place(sk[warp], cs, a.rot, a.interleaved, lane);
+        __syncwarp();
+      }
+      for (int j = lane; j < D; j += 32) {
+        sq[warp][j] *= fq;
+        sk[warp][j] *= fk;
+      }
+      if (MODE == 1 && lane == 0) {
+        const float x = a.ab[(size_t)row * 2 * H + h], y = a.ab[(size_t)row * 2 * H + H + h];
+        sg[warp] = expf(-A * softplus_f(x + dt));
+        sb[warp] = sigmoid_f(y);
+      }
+    }
+    for (int i = threadIdx.x; i < nt * cols; i += SCAN_THREADS) {
+      const int tt = i / cols, cc = i % cols;
+      const int col = blockIdx.x * cols + cc;
+      sv[tt][cc] = col < V ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * V + col]) : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float v = sv[tt][col_local];
+      const float *kq = sk[tt], *qq = sq[tt];
+      float o = 0.f;
+      if (MODE == 0) {
+#pragma unroll
+        for (int r = 0; r < SCAN_R; ++r) {
+          if (r < R) {
+            const int d = r * L + lane_in_col;
+            const float kd = d < D ? kq[d] : 0.f, qd = d < D ? qq[d] : 0.f;
+            S[r] = fmaf(decay, S[r], kd * v);
+            o = fmaf(S[r], qd, o);
+          }
+        }
+      } else {
+        const float g = sg[tt], beta = sb[tt];
+        float dot = 0.f;
+#pragma unroll
+        for (int r = 0; r < SCAN_R; ++r) {
+          if (r < R) {
+            const int d = r * L + lane_in_col;
+            S[r] *= g;
+            dot = fmaf(S[r], d < D ? kq[d] : 0.f, dot);
+          }
+        }
+        for (int off = L >> 1; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        const float u = beta * (v - dot);
+#pragma unroll
+        for (int r = 0; r < SCAN_R; ++r) {
+          if (r < R) {
+            const int d = r * L + lane_in_col;
+            const float kd = d < D ? kq[d] : 0.f, qd = d < D ? qq[d] : 0.f;
+            S[r] = fmaf(kd, u, S[r]);
+            o = fmaf(S[r], qd, o);
+          }
+        }
+      }
+      for (int off = L >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (live && lane_in_col == 0) a.out[(size_t)(first_row + t0 + tt) * H * V + (size_t)h * V + c] = o;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < SCAN_R; ++r) {
+      const int d = r * L + lane_in_col;
+      if (r < R && d < D) sp[d] = S[r];
+    }
+  }
+}
+
+extern "C" int g2b_state_scan(int mode, int dtype, const void *q, int q_stride, const void *k, int k_stride,
+                              const void *v, int v_stride, int H, int G, int D, int V, const float *rope, int rot,
+                              int interleaved, float q_scale, float k_scale, int unit_norm, float unit_eps,
+                              const float *decay, const float *ab, const float *A_log, const float *dt_bias,
+                              float *state, const int *tok_pos, const int *seq_slots, const int *seq_meta,
+                              int n_tokens, int n_seqs, float *out, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_seqs <= 0) return 0;
+  if (D <= 0 || D > SCAN_MAX_D) G2B_REFUSE("state_scan: key size %d outside 1..%d", D, SCAN_MAX_D);
+  if (G <= 0 || H % G) G2B_REFUSE("state_scan: %d heads are not a multiple of %d query/key heads", H, G);
+  if (rope && (rot <= 0 || rot > D || (rot & 1))) G2B_REFUSE("state_scan: %d rotated entries of a head of %d", rot, D);
+  if (mode == 0 ? !decay : (!ab || !A_log || !dt_bias)) G2B_REFUSE("state_scan: mode %d lacks its decay inputs", mode);
+  int L = 8;
+  while (L * SCAN_R < D) L <<= 1;                 // 8, 16 or 32 lanes a column
+  ScanArgs a;
+  a.q = q; a.k = k; a.v = v; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
+  a.H = H; a.G = G; a.D = D; a.V = V; a.rope = (const float2 *)rope; a.rot = rot; a.interleaved = interleaved;
+  a.q_scale = q_scale; a.k_scale = k_scale; a.unit_norm = unit_norm; a.unit_eps = unit_eps; a.decay = decay;
+  a.ab = ab; a.A_log = A_log; a.dt_bias = dt_bias; a.state = state; a.tok_pos = tok_pos; a.seq_slots = seq_slots;
+  a.seq_meta = seq_meta; a.out = out; a.n_tokens = n_tokens;
+  const int cols = SCAN_THREADS / L;
+  const dim3 grid((V + cols - 1) / cols, H, n_seqs);
+  if (dtype != G2B_F32 && dtype != G2B_BF16) G2B_REFUSE("state_scan: unknown dtype %d", dtype);
+  if (mode == 0) {
+    if (dtype == G2B_F32) g2b_launch(state_scan_kernel<float, 0>, grid, dim3(SCAN_THREADS), 0, stream, a, L);
+    else g2b_launch(state_scan_kernel<bf16, 0>, grid, dim3(SCAN_THREADS), 0, stream, a, L);
+  } else if (mode == 1) {
+    if (dtype == G2B_F32) g2b_launch(state_scan_kernel<float, 1>, grid, dim3(SCAN_THREADS), 0, stream, a, L);
+    else g2b_launch(state_scan_kernel<bf16, 1>, grid, dim3(SCAN_THREADS), 0, stream, a, L);
+  } else {
+    G2B_REFUSE("state_scan: unknown mode %d", mode);
+  }
+  return g2b_check_launch("state_scan");
+}
+
+// ---------------------------------------------------------------------------
+// per-head norm of the scan's output, times a gate
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float *__restrict__ o, int T_tokens, int H, int V, const float *__restrict__ w, float eps,
+                      const T *__restrict__ gate, int gate_stride, float out_scale, T *__restrict__ out) {
+  pdl_launch();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * 4 + warp;
+  if (item >= (long long)T_tokens * H) return;
+  const int t = (int)(item / H), h = (int)(item % H);
+  const float *p = o + (size_t)t * H * V + (size_t)h * V;
+  float ss = 0.f;
+  for (int j = lane; j < V; j += 32) ss = fmaf(p[j], p[j], ss);
+  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)V + eps);
+  for (int j = lane; j < V; j += 32) {
+    float y = p[j] * inv;
+    if (w) y *= w[j];
+    if (gate) y *= silu_f(to_f32(gate[(size_t)t * gate_stride + (size_t)h * V + j]));
+    out[(size_t)t * H * V + (size_t)h * V + j] = from_f32<T>(y * out_scale);
+  }
+}
+
+extern "C" int g2b_head_norm_gate(const float *o, int T_tokens, int H, int V, const float *w, float eps,
+                                  const void *gate, int gate_stride, int dtype, float out_scale, void *out,
+                                  cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  const unsigned blocks = (unsigned)(((long long)T_tokens * H + 3) / 4);
+  if (dtype == G2B_F32)
+    g2b_launch(head_norm_gate_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, T_tokens, H, V, w, eps,
+               (const float *)gate, gate_stride, out_scale, (float *)out);
+  else if (dtype == G2B_BF16)
+    g2b_launch(head_norm_gate_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, o, T_tokens, H, V, w, eps,
+               (const bf16 *)gate, gate_stride, out_scale, (bf16 *)out);
+  else
+    G2B_REFUSE("head_norm_gate: unknown dtype %d", dtype);
+  return g2b_check_launch("head_norm_gate");
+}
+
+// ---------------------------------------------------------------------------
+// attention output times sigmoid(gate), element by element; heads lose their padding
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_mul_kernel(const T *__restrict__ o, int hd, const T *__restrict__ gate, int gate_stride, int T_tokens, int H, int V,
+                float out_scale, T *__restrict__ out) {
+  pdl_launch();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = H * V;
+  if (i >= (long long)T_tokens * n) return;
+  const int t = (int)(i / n), r = (int)(i % n), h = r / V, j = r % V;
+  float y = to_f32(o[(size_t)t * H * hd + (size_t)h * hd + j]);
+  if (gate) y *= sigmoid_f(to_f32(gate[(size_t)t * gate_stride + r]));
+  out[i] = from_f32<T>(y * out_scale);
+}
+
+extern "C" int g2b_gate_mul(const void *o, int hd, const void *gate, int gate_stride, int dtype, int T_tokens, int H,
+                            int V, float out_scale, void *out, cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  const unsigned blocks = (unsigned)(((long long)T_tokens * H * V + 255) / 256);
+  if (dtype == G2B_F32)
+    g2b_launch(gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *)o, hd, (const float *)gate,
+               gate_stride, T_tokens, H, V, out_scale, (float *)out);
+  else if (dtype == G2B_BF16)
+    g2b_launch(gate_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16 *)o, hd, (const bf16 *)gate,
+               gate_stride, T_tokens, H, V, out_scale, (bf16 *)out);
+  else
+    G2B_REFUSE("gate_mul: unknown dtype %d", dtype);
+  return g2b_check_launch("gate_mul");
+}
+
+// ---------------------------------------------------------------------------
+// x += norm(y) * w; the new x once more in the compute type
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_add_kernel(float *__restrict__ x, const float *__restrict__ y, const float *__restrict__ w, float eps, int Hw,
+                T *__restrict__ cast_out) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  float *xr = x + (size_t)t * Hw;
+  float inv = 0.f;
+  if (y) {
+    const float *yr = y + (size_t)t * Hw;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < Hw; j += blockDim.x) ss = fmaf(yr[j], yr[j], ss);
+    ss = block_sum(ss, scratch);
+    inv = 1.f / sqrtf(ss / (float)Hw + eps);
+  }
+  for (int j = threadIdx.x; j < Hw; j += blockDim.x) {
+    float v = xr[j];
+    if (y) {
+      v += (y[(size_t)t * Hw + j] * inv) * (w ? w[j] : 1.f);
+      xr[j] = v;
+    }
+    if (cast_out) cast_out[(size_t)t * Hw + j] = from_f32<T>(v);
+  }
+}
+
+extern "C" int g2b_norm_add(float *x, const float *y, const float *w, float eps, int T_tokens, int Hw, void *cast_out,
+                            int dtype, cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (dtype == G2B_F32)
+    g2b_launch(norm_add_kernel<float>, dim3(T_tokens), dim3(256), 0, stream, x, y, w, eps, Hw, (float *)cast_out);
+  else if (dtype == G2B_BF16)
+    g2b_launch(norm_add_kernel<bf16>, dim3(T_tokens), dim3(256), 0, stream, x, y, w, eps, Hw, (bf16 *)cast_out);
+  else
+    G2B_REFUSE("norm_add: unknown dtype %d", dtype);
+  return g2b_check_launch("norm_add");
+}

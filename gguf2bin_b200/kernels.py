@@ -18,7 +18,9 @@ from .csrc.build import KernelBuildError, KernelError, load_unit
 __all__ = ["KernelError", "KernelBuildError", "embed_rows", "rmsnorm", "qknorm_rope_cache",
            "rope_table", "cache_write", "swiglu", "advance_positions", "gemm_simt", "linear", "attn_generic",
            "attention", "sample_rows", "sample_filtered", "recent_set", "seed_slots", "embed_pair_norm",
-           "canon_conv", "norm_canon_single", "latent_keep", "head_product", "head_gate", "gated_add", "xielu"]
+           "canon_conv", "norm_canon_single", "latent_keep", "head_product", "head_gate", "gated_add", "xielu",
+           "proj_norm_rope_cache", "rotate_heads", "short_conv", "state_scan", "head_norm_gate", "gate_mul",
+           "norm_add", "moe_route", "moe_plan", "moe_gemm", "moe_combine", "moe_tile_rows"]
 
 F32, BF16 = 0, 1
 EPI_STORE_F32, EPI_STORE_BF16, EPI_ACCUM_F32 = 0, 1, 2
@@ -436,16 +438,17 @@ def attention_notices(what: str, head_dim: int, page_size: int, compute_dtype: t
 # attention
 # ---------------------------------------------------------------------------
 def attn_generic(q, out, cache_pages, tok_pos, tok_seq, page_table, n_heads, n_kv_heads,
-                 head_dim, page_size, window, scale, sink=None, planes: int = 2, gate=None) -> None:
+                 head_dim, page_size, window, scale, sink=None, planes: int = 2, gate=None, chunk: int = 0) -> None:
     """Causal attention of every token of the step over its sequence's cache pages,
     32-bit arithmetic; q [T, n_heads*head_dim] (rows may lie further apart: columns of a wider
     buffer), out [T, n_heads*head_dim] contiguous.  ``sink`` (float32 [n_heads]): one more
     term exp(sink_h) in each head's softmax denominator.  ``planes`` = 1: the pages hold one
     panel per kv head that is read as keys and as values.  ``gate`` [T, n_heads] (rows may lie
-    further apart): every head's output is multiplied by the sigmoid of its gate."""
+    further apart): every head's output is multiplied by the sigmoid of its gate.  ``chunk`` > 0:
+    a token sees the keys of its own chunk of that many positions only (counted from position 0)."""
     f = _fn("attn_generic.cu", "g2b_attn_generic",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
     if q.dtype != cache_pages.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, out and the cache must have one dtype")
     if q.stride(1) != 1 or not out.is_contiguous() or (gate is not None and (gate.stride(1) != 1 or gate.dtype != q.dtype)):
@@ -455,19 +458,19 @@ def attn_generic(q, out, cache_pages, tok_pos, tok_seq, page_table, n_heads, n_k
     _call(f, _ptr(q), _ptr(out), _code(q.dtype), _ptr(cache_pages), _ptr(tok_pos), _ptr(tok_seq),
           _ptr(page_table), page_table.shape[1], q.shape[0], n_heads, n_kv_heads, head_dim,
           page_size, window, scale, _ptr(sink), planes, q.stride(0), _ptr(gate),
-          gate.stride(0) if gate is not None else 0, _stream())
+          gate.stride(0) if gate is not None else 0, int(chunk), _stream())
 
 
 def attention(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-              scale, sink=None, planes: int = 2, gate=None) -> None:
+              scale, sink=None, planes: int = 2, gate=None, chunk: int = 0) -> None:
     """Attention of a step: the tensor-core kernels when they take the case, else the
     32-bit kernel.  ``q`` and ``gate`` may be column ranges of a wider buffer."""
-    if q.dtype == torch.bfloat16:
+    if q.dtype == torch.bfloat16 and not chunk:
         if (_bf16 or _bf16_mod()).attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim,
                                        page_size, window, scale, sink, planes, gate):
             return
     attn_generic(q, out, cache_pages, ctx.tok_pos, ctx.tok_seq, ctx.page_table, n_heads,
-                 n_kv_heads, head_dim, page_size, window, scale, sink, planes, gate)
+                 n_kv_heads, head_dim, page_size, window, scale, sink, planes, gate, chunk)
 
 
 def normed_product(x32, eps, w, out, gate_block=None) -> bool:
@@ -564,3 +567,174 @@ def seed_slots(seq_state, slots, streams, seed: int) -> None:
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_ulonglong, c_void_p])
     _call(f, _ptr(seq_state), seq_state.shape[1], _ptr(slots), _ptr(streams), slots.shape[0],
           seed & 0xFFFFFFFFFFFFFFFF, _stream())
+
+
+# ---------------------------------------------------------------------------
+# seq_mix.cu: mixers with a matrix state, their short convolution, a wide attention prologue
+# ---------------------------------------------------------------------------
+def _dense_rows(t: torch.Tensor, what: str) -> int:
+    if t.stride(1) != 1:
+        raise KernelError(f"{what}: rows must be dense (they may lie apart)")
+    return t.stride(0)
+
+
+def proj_norm_rope_cache(qkv, bias, n_heads, n_kv_heads, qk_dim, v_dim, q_w, k_w, eps, rope, rotary_dim,
+                         interleaved, ctx, cache_pages, page_size, q_out) -> None:
+    """q, k, v side by side in ``qkv`` [T, nh*D + nkv*D + nkv*V] (+ ``bias``, float32); RMS norm over
+    ALL of q and over all of k (weights ``q_w`` [nh*D], ``k_w`` [nkv*D]; None: no norm); rotation by
+    the step's ``rope`` table, pairs (i, i + r/2) or, ``interleaved``, (2i, 2i + 1); q to ``q_out``
+    [T, nh*hd] and k, v into the pages, heads zero-filled to hd = max(D, V)."""
+    f = _fn("seq_mix.cu", "g2b_proj_norm_rope_cache",
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+             c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p])
+    if q_out.dtype != qkv.dtype or cache_pages.dtype != qkv.dtype or not q_out.is_contiguous():
+        raise KernelError("proj_norm_rope_cache: q_out and the cache must have the input's dtype")
+    for t in (bias, q_w, k_w):
+        if t is not None:
+            _need(t, torch.float32, "bias / norm weight")
+    _call(f, _ptr(qkv), _code(qkv.dtype), _dense_rows(qkv, "qkv"), qkv.shape[0], _ptr(bias), n_heads, n_kv_heads,
+          qk_dim, v_dim, _ptr(q_w), _ptr(k_w), eps, _ptr(rope), rotary_dim, 1 if interleaved else 0,
+          _ptr(ctx.tok_pos), _ptr(ctx.tok_seq), _ptr(ctx.page_table), ctx.page_table.shape[1],
+          _ptr(cache_pages), page_size, _ptr(q_out), _stream())
+
+
+def rotate_heads(x, heads, head_dim, rope, rotary_dim, interleaved, scale: float = 1.0) -> None:
+    """In place: the first ``rotary_dim`` entries of every head of x [T, heads*head_dim] (rows may lie
+    apart) turn by the step's ``rope`` table; then everything times ``scale``."""
+    f = _fn("seq_mix.cu", "g2b_rotate_heads",
+            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
+    _call(f, _ptr(x), _code(x.dtype), _dense_rows(x, "x"), x.shape[0], heads, head_dim, _ptr(rope), rotary_dim,
+          1 if interleaved else 0, scale, _stream())
+
+
+def short_conv(x, w32, ring, ctx, out, act: bool = True) -> None:
+    """out_t = act(sum_j w32[j, c] * x_{t - taps + 1 + j}[c]) per channel, act = SiLU; ``w32`` float32
+    [taps, C]; ``ring`` [slots, taps, C] holds every sequence's last input rows by position mod taps
+    and is brought up to date (in the same launch for a step of one token per sequence)."""
+    taps, C = w32.shape
+    _need(w32, torch.float32, "convolution weights")
+    if out.dtype != x.dtype or (ring is not None and ring.dtype != x.dtype):
+        raise KernelError("short_conv: input, output and ring must have one dtype")
+    f = _fn("seq_mix.cu", "g2b_short_conv",
+            [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_void_p, c_int, c_void_p])
+    _call(f, _ptr(x), _code(x.dtype), _dense_rows(x, "x"), _ptr(w32), _ptr(ring), taps, C, x.shape[0], ctx.n_seqs,
+          _ptr(ctx.tok_pos), _ptr(ctx.tok_seq), _ptr(ctx.seq_slots), _ptr(ctx.seq_meta), 1 if act else 0,
+          _ptr(out), _dense_rows(out, "out"), _stream())
+    if ctx.seq_meta is not None and taps > 1:
+        count_launches(1)
+
+
+def state_scan(q, k, v, state, ctx, out32, heads, qk_heads, qk_dim, v_dim, *, decay=None, ab=None, a_log=None,
+               dt_bias=None, rope=None, rotary_dim: int = 0, interleaved: bool = False, q_scale: float = 1.0,
+               k_scale: float = 1.0, unit_eps: Optional[float] = None) -> None:
+    """The recurrence of a mixer with a matrix state per head, over the step's tokens in order;
+    ``state`` float32 [slots, heads, v_dim, qk_dim] is read and left up to date.  ``decay`` (float32
+    [heads]): S = a S + k v^T.  Otherwise ``ab`` (float32 [T, 2*heads]: x then y), ``a_log``, ``dt_bias``:
+    S = g S with g = exp(-exp(a_log) softplus(x + dt_bias)); u = sigmoid(y) (v - S^T k); S += k u^T.
+    Either way o = S^T q, float32 into ``out32`` [T, heads*v_dim].  q and k first turn by ``rope``
+    (or, with ``unit_eps``, are divided by sqrt(sum x^2 + unit_eps)), then take their scales."""
+    T = q.shape[0]
+    _need(state, torch.float32, "state")
+    _need(out32, torch.float32, "scan output")
+    mode = 0 if decay is not None else 1
+    for t in (decay, ab, a_log, dt_bias):
+        if t is not None:
+            _need(t, torch.float32, "decay inputs")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise KernelError("state_scan: q, k and v must have one dtype")
+    f = _fn("seq_mix.cu", "g2b_state_scan",
+            [c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+             c_int, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _call(f, mode, _code(q.dtype), _ptr(q), _dense_rows(q, "q"), _ptr(k), _dense_rows(k, "k"), _ptr(v),
+          _dense_rows(v, "v"), heads, qk_heads, qk_dim, v_dim, _ptr(rope), rotary_dim, 1 if interleaved else 0,
+          q_scale, k_scale, 0 if unit_eps is None else 1, unit_eps or 0.0, _ptr(decay), _ptr(ab), _ptr(a_log),
+          _ptr(dt_bias), _ptr(state), _ptr(ctx.tok_pos), _ptr(ctx.seq_slots), _ptr(ctx.seq_meta), T, ctx.n_seqs,
+          _ptr(out32), _stream())
+
+
+def head_norm_gate(o32, heads, v_dim, w, eps, gate, out_scale, out) -> None:
+    """out = o / sqrt(mean(o^2) + eps) per head (times ``w`` [v_dim], float32, if given), times
+    silu(gate) (if given; [T, heads*v_dim], rows may lie apart), times ``out_scale``."""
+    _need(o32, torch.float32, "scan output")
+    if w is not None:
+        _need(w, torch.float32, "head norm weight")
+    f = _fn("seq_mix.cu", "g2b_head_norm_gate",
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p])
+    if gate is not None and gate.dtype != out.dtype:
+        raise KernelError("head_norm_gate: gate and output must have one dtype")
+    _call(f, _ptr(o32), o32.shape[0], heads, v_dim, _ptr(w), eps, _ptr(gate),
+          _dense_rows(gate, "gate") if gate is not None else 0, _code(out.dtype), out_scale, _ptr(out), _stream())
+
+
+def gate_mul(o, head_dim, gate, heads, v_dim, out_scale, out) -> None:
+    """out[t, h*v_dim + j] = o[t, h*head_dim + j] * sigmoid(gate[t, h*v_dim + j]) * out_scale."""
+    f = _fn("seq_mix.cu", "g2b_gate_mul",
+            [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    if out.dtype != o.dtype or (gate is not None and gate.dtype != o.dtype) or not o.is_contiguous():
+        raise KernelError("gate_mul: one dtype, and a contiguous input")
+    _call(f, _ptr(o), head_dim, _ptr(gate), _dense_rows(gate, "gate") if gate is not None else 0, _code(o.dtype),
+          o.shape[0], heads, v_dim, out_scale, _ptr(out), _stream())
+
+
+def norm_add(x32, y32, w, eps, cast_out=None) -> None:
+    """x += y / sqrt(mean(y^2) + eps) * w (float32; ``w`` None: no weight); the new x once more,
+    rounded, into ``cast_out``.  ``y32`` None: only the rounding."""
+    _need(x32, torch.float32, "stream")
+    if y32 is not None:
+        _need(y32, torch.float32, "sublayer output")
+    if w is not None:
+        _need(w, torch.float32, "norm weight")
+    f = _fn("seq_mix.cu", "g2b_norm_add",
+            [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_void_p])
+    _call(f, _ptr(x32), _ptr(y32), _ptr(w), eps, x32.shape[0], x32.shape[1], _ptr(cast_out),
+          _code(cast_out.dtype) if cast_out is not None else F32, _stream())
+
+
+# ---------------------------------------------------------------------------
+# moe.cu: a routed feed-forward
+# ---------------------------------------------------------------------------
+def moe_tile_rows() -> int:
+    lib = load_unit("moe.cu")
+    return int(lib.g2b_moe_tile_rows())
+
+
+def moe_route(z32, correction, top: int, renormalise: bool, idx, weight) -> None:
+    """softmax over all experts of ``z32`` [T, N]; the ``top`` largest of score + correction chosen
+    (``idx`` int32 [T, top]); ``weight`` float32 [T, top] their scores (divided by their sum when
+    ``renormalise``)."""
+    _need(z32, torch.float32, "router logits")
+    _need(idx, torch.int32, "idx")
+    _need(weight, torch.float32, "weight")
+    f = _fn("moe.cu", "g2b_moe_route", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _call(f, _ptr(z32), _ptr(correction), z32.shape[0], z32.shape[1], top, 1 if renormalise else 0, _ptr(idx),
+          _ptr(weight), _stream())
+
+
+def moe_plan(idx, n_real: int, max_tiles: int, plan, row_pair, pair_row) -> None:
+    """Groups the (token, choice) pairs of ``idx`` by expert; experts from ``n_real`` on get no rows."""
+    f = _fn("moe.cu", "g2b_moe_plan", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _call(f, _ptr(idx), idx.numel(), n_real, moe_tile_rows(), max_tiles, _ptr(plan), _ptr(row_pair), _ptr(pair_row),
+          _stream())
+
+
+def moe_gemm(a, row_pair, pairs_per_token: int, w, n_out: int, plan, n_real: int, max_tiles: int, swiglu: bool,
+             out) -> None:
+    """Per expert e over its rows: out[row] = a[source of row] . w[e]^T; ``w`` [E, n_out (x2: gate rows
+    then up rows, with ``swiglu``), K]; ``row_pair`` None: row r reads a[r]."""
+    if w.dtype != a.dtype:
+        raise KernelError("moe_gemm: activations and expert matrices must have one dtype")
+    f = _fn("moe.cu", "g2b_moe_gemm",
+            [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
+             c_void_p, c_int, c_void_p])
+    _call(f, _ptr(a), _code(a.dtype), _dense_rows(a, "a"), _ptr(row_pair), pairs_per_token, _ptr(w), n_out,
+          a.shape[1], _ptr(plan), n_real, max_tiles, 1 if swiglu else 0, _ptr(out),
+          1 if out.dtype == torch.float32 else 0, _stream())
+
+
+def moe_combine(rows32, pair_row, weight, x_self32, top: int, out32) -> None:
+    """out[t] = sum_j weight[t, j] * (rows32[pair_row[t, j]], or x_self32[t] where the pair has no row)."""
+    f = _fn("moe.cu", "g2b_moe_combine", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _call(f, _ptr(rows32), _ptr(pair_row), _ptr(weight), _ptr(x_self32), out32.shape[0], top, out32.shape[1],
+          _ptr(out32), _stream())

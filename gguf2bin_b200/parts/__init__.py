@@ -5,7 +5,7 @@ from .registry import (block_class, embedding_class, feed_forward_class, head_cl
                        norm_class, position_class, register_block, register_embedding,
                        register_feed_forward, register_head, register_mixer, register_norm,
                        register_position, registered)
-from . import norms, positions, mixers, latent, feed_forward, blocks, ends  # noqa: F401  (registration)
+from . import norms, positions, mixers, latent, recurrent, feed_forward, blocks, ends  # noqa: F401  (registration)
 
 __all__ = ["StepContext", "block_class", "embedding_class", "feed_forward_class", "head_class",
            "mixer_class", "norm_class", "position_class", "register_block", "register_embedding",

@@ -1,5 +1,7 @@
 """Block arrangements.  ``prenorm``: x += mixer(norm(x)); x += feed_forward(norm(x)), the
 residual stream kept in float32 (src/l5_model.c:494-597 of AnonymoDGH/gguf2bin).
+``branch_norm``: x += norm(mixer(x)); x += norm(feed_forward(x)): the norm sits on each sublayer's
+OUTPUT and the sublayers read the stream itself.
 ``gated_prenorm``: the same with each sublayer's result scaled by a learned gate, an optional
 short convolution over time in front of the mixer, and an optional feed-forward."""
 from __future__ import annotations
@@ -10,6 +12,7 @@ from .. import kernels
 from ..cache.storage import StateNeed
 from ..config.specs import LayerSpec
 from ..weights.loader import Expected
+from .feed_forward import RoutedExperts
 from .norms import RMSNorm
 from .registry import (feed_forward_class, mixer_class, norm_class, register_block)
 
@@ -85,6 +88,103 @@ class PreNormBlock:
             h = ctx.workspace.buffer("block.normed", (T, self.hidden), self.dtype)
             self.ffn_norm.forward(x32, h)
             self.feed_forward.forward(h, ctx, x32)
+
+
+class BranchNormBlock:
+    """``branch_norm``: x <- x + norm1(mixer(x)), then x <- x + norm2(feed_forward(x)).  The
+    sublayers read the stream as it is (rounded to the compute type for their products); each
+    sublayer's whole output is normed, in 32-bit, before it joins the stream.  A layer may have no
+    feed-forward.  Any mixer or feed-forward of the library fits: a part adds into a cleared
+    32-bit buffer, or stores there when it offers ``forward_into``."""
+
+    def __init__(self, layer: LayerSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.names = dict(layer.block["names"])
+        self.hidden, self.dtype = int(hidden_size), dtype
+        ffn_norm = layer.ffn_norm or layer.norm
+        self.mixer_norm = norm_class(layer.norm)(layer.norm, hidden_size, dtype, device)
+        self.mixer = mixer_class(layer.mixer)(layer.mixer, hidden_size, dtype, device)
+        self.feed_forward = self.ffn_norm = None
+        if layer.feed_forward is not None:
+            self.ffn_norm = norm_class(ffn_norm)(ffn_norm, hidden_size, dtype, device)
+            self.feed_forward = feed_forward_class(layer.feed_forward)(layer.feed_forward, hidden_size,
+                                                                       dtype, device)
+
+    @classmethod
+    def expected(cls, layer: LayerSpec, hidden_size: int) -> dict:
+        names = dict(layer.block["names"])
+        out = {}
+        out.update(norm_class(layer.norm).expected(layer.norm, hidden_size, names["mixer_norm"]))
+        out.update(mixer_class(layer.mixer).expected(layer.mixer, hidden_size))
+        ffn_norm = layer.ffn_norm or layer.norm
+        second = norm_class(ffn_norm).expected(ffn_norm, hidden_size, names["ffn_norm"])
+        if layer.feed_forward is not None:
+            out.update(second)
+            out.update(feed_forward_class(layer.feed_forward).expected(layer.feed_forward, hidden_size))
+        else:        # a checkpoint may carry the second norm all the same; it is unused
+            out.update({k: Expected(e.shape, e.init, optional=True) for k, e in second.items()})
+        return out
+
+    def bind(self, tensors: dict) -> None:
+        self.mixer_norm.bind(tensors[self.names["mixer_norm"]])
+        self.mixer.bind(tensors)
+        if self.feed_forward is not None:
+            self.ffn_norm.bind(tensors[self.names["ffn_norm"]])
+            self.feed_forward.bind(tensors)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def parts(self) -> tuple:
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) if p is not None)
+
+    def weights(self):
+        for part in self.parts():
+            yield from getattr(part, "weights", tuple)()
+
+    def notices(self) -> list:
+        return [line for part in self.parts() for line in getattr(part, "notices", list)()]
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", False) for part in self.parts())
+
+    def _join(self, x32, y, norm, h_next) -> None:
+        """x += norm(y), and the new x rounded for the next reader."""
+        w = getattr(norm, "weight", None)
+        if isinstance(norm, RMSNorm):
+            kernels.norm_add(x32, y, w, norm.eps, h_next)
+            return
+        normed = torch.empty_like(y)               # another kind of norm: its own kernel, then the sum
+        norm.forward(y, normed)
+        x32.add_(normed)
+        if h_next is not None:
+            h_next.copy_(x32)
+
+    def forward(self, x32: torch.Tensor, ctx, cache_view) -> None:
+        T, H, ws = x32.shape[0], self.hidden, ctx.workspace
+        h = ctx.step_cache.pop(("branch_norm.rounded", x32.data_ptr()), None)
+        if h is None:                              # the block in front left no rounded copy of the stream
+            h = ws.buffer("branch.input", (T, H), self.dtype)
+            kernels.norm_add(x32, None, None, 0.0, h)
+        y = ws.buffer("branch.result", (T, H), torch.float32)
+        y.zero_()
+        self.mixer.forward(h, ctx, cache_view, y)
+        last = self.feed_forward is None
+        follows = isinstance(getattr(ctx, "next_block", None), BranchNormBlock)
+        self._join(x32, y, self.mixer_norm, h if (not last or follows) else None)
+        if not last:
+            ff = self.feed_forward
+            if hasattr(ff, "forward_into"):
+                if isinstance(ff, RoutedExperts):
+                    ff.forward_into(h, ctx, y, x32)
+                else:
+                    ff.forward_into(h, ctx, y)
+            else:
+                y.zero_()
+                ff.forward(h, ctx, y)
+            self._join(x32, y, self.ffn_norm, h if follows else None)
+        if follows:
+            ctx.step_cache[("branch_norm.rounded", x32.data_ptr())] = h
 
 
 PENDING = "gated_prenorm.owed"        # key of a step's left-over gated addition in StepContext.step_cache
@@ -260,3 +360,4 @@ class GatedPreNormBlock:
 
 register_block("prenorm", PreNormBlock)
 register_block("gated_prenorm", GatedPreNormBlock)
+register_block("branch_norm", BranchNormBlock)

@@ -147,5 +147,101 @@ class ActMLP:
         kernels.linear(mid, self.w_down, out32, accumulate=accumulate)
 
 
+class RoutedExperts:
+    """``routed_experts``: ``n_experts`` small gated feed-forwards, down(silu(gate h) * (up h)) without
+    biases, of which every token uses ``top``.  Router logits z = W_r h over ``n_experts + n_identity``
+    outputs and their softmax are 32-bit; the ``top`` largest of score + ``correction`` (a stored
+    vector that steers the choice and nothing else; optional) are chosen; a chosen expert's weight is
+    its score as it is (``renormalise``: divided by the chosen scores' sum).  The last ``n_identity``
+    router outputs stand for experts without matrices whose output is their input.  The result is
+    the weighted sum of the chosen experts' outputs, added in the order of the choice.
+
+    A step groups its (token, choice) pairs by expert on the device (``moe_plan``) and runs one
+    grouped product for gate and up with the activation in its epilogue and one for down; nothing
+    comes back to the host, so the step may be replayed from a CUDA graph."""
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.E, self.I = int(spec["n_experts"]), int(spec.get("n_identity") or 0)
+        self.top, self.inter = int(spec["top"]), int(spec["intermediate_size"])
+        self.hidden, self.dtype, self.device = int(hidden_size), dtype, device
+        self.renormalise = bool(spec.get("renormalise") or False)
+        self.has_correction = bool(spec.get("correction") or False)
+        if self.E < 0 or self.I < 0 or not (1 <= self.top <= self.E + self.I) or self.E > 1024:
+            raise ConfigError(f"routed_experts: {self.top} choices among {self.E} + {self.I} experts")
+        self.names = dict(spec["names"])
+        self.w_router = self.correction = self.w_gate_up = self.w_down = None
+
+    @classmethod
+    def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
+        n, inter = dict(spec["names"]), spec["intermediate_size"]
+        E, I = int(spec["n_experts"]), int(spec.get("n_identity") or 0)
+        out = {n["router"]: Expected((E + I, hidden_size))}
+        if spec.get("correction"):
+            out[n["correction"]] = Expected((E + I,))
+        for e in range(E):
+            out[n["gate"].format(e)] = Expected((inter, hidden_size))
+            out[n["up"].format(e)] = Expected((inter, hidden_size))
+            out[n["down"].format(e)] = Expected((hidden_size, inter))
+        return out
+
+    def bind(self, tensors: dict) -> None:
+        n = self.names
+        self.w_router = tensors[n["router"]].contiguous()
+        if self.has_correction:
+            self.correction = tensors[n["correction"]].to(torch.float32).contiguous()
+        if self.E:
+            mats = [tensors[n[k].format(e)] for e in range(self.E) for k in ("gate", "up", "down")]
+            common = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
+            # per expert: gate rows, then up rows
+            self.w_gate_up = torch.stack([torch.cat([tensors[n["gate"].format(e)].to(common),
+                                                     tensors[n["up"].format(e)].to(common)], dim=0)
+                                          for e in range(self.E)]).contiguous()
+            self.w_down = torch.stack([tensors[n["down"].format(e)].to(common) for e in range(self.E)]).contiguous()
+
+    def weights(self):
+        return tuple(t for t in (self.w_router, self.correction, self.w_gate_up, self.w_down) if t is not None)
+
+    def notices(self) -> list:
+        if self.w_gate_up is not None and self.dtype == torch.bfloat16 and \
+                (self.w_gate_up.dtype != torch.bfloat16 or self.hidden % 8 or self.inter % 8):
+            return ["routed experts: matrices kept in 32-bit, or sizes that are no multiple of 8: their "
+                    "products run on the CUDA cores, not on the tensor cores"]
+        return []
+
+    def forward(self, h: torch.Tensor, ctx, residual32: torch.Tensor, x_self32: torch.Tensor = None) -> None:
+        y = ctx.workspace.buffer("moe.sum", tuple(residual32.shape), torch.float32)
+        self.forward_into(h, ctx, y, x_self32)
+        residual32.add_(y)
+
+    def forward_into(self, h: torch.Tensor, ctx, out32: torch.Tensor, x_self32: torch.Tensor = None) -> None:
+        """Stores the result.  ``x_self32``: the input in 32-bit, for the experts whose output is their
+        input (default: ``h`` widened)."""
+        T, ws, top, E = h.shape[0], ctx.workspace, self.top, self.E
+        z = ws.buffer("moe.logits", (T, E + self.I), torch.float32)
+        kernels.linear(h, self.w_router, z)
+        idx = ws.buffer("moe.idx", (T, top), torch.int32)
+        weight = ws.buffer("moe.weight", (T, top), torch.float32)
+        kernels.moe_route(z, self.correction, top, self.renormalise, idx, weight)
+        n_pairs = T * top
+        tile = kernels.moe_tile_rows()
+        max_tiles = -(-n_pairs // tile) + E               # every expert's last tile may be part full
+        plan = ws.buffer("moe.plan", (E + 2 + 3 * max_tiles,), torch.int32)
+        row_pair = ws.buffer("moe.row_pair", (n_pairs,), torch.int32)
+        pair_row = ws.buffer("moe.pair_row", (n_pairs,), torch.int32)
+        kernels.moe_plan(idx, E, max_tiles, plan, row_pair, pair_row)
+        rows32 = ws.buffer("moe.rows", (n_pairs, self.hidden), torch.float32)
+        if E:
+            wt = self.w_gate_up.dtype                     # matrices stored in 32-bit keep their products there
+            mid = ws.buffer("moe.mid", (n_pairs, self.inter), wt)
+            a = h if h.dtype == wt else h.to(wt)
+            kernels.moe_gemm(a, row_pair, top, self.w_gate_up, self.inter, plan, E, max_tiles, True, mid)
+            kernels.moe_gemm(mid, None, 1, self.w_down, self.hidden, plan, E, max_tiles, False, rows32)
+        if x_self32 is None:
+            x_self32 = h if h.dtype == torch.float32 else h.float()
+        kernels.moe_combine(rows32, pair_row, weight, x_self32, top, out32)
+
+
+register_feed_forward("routed_experts", RoutedExperts)
 register_feed_forward("swiglu", SwiGLU)
 register_feed_forward("act_mlp", ActMLP)

@@ -9,6 +9,21 @@ encoding of q and k; k (normed, rotated) and v (raw) written to the cache; score
 With ``shared_kv`` the mixer has no k and v projections and writes nothing: it attends
 over the keys and values that another layer stored (the schedule entry's ``cache_of``
 names that layer, whose kv heads and head size it must share).
+
+Further options, each a parameter of the spec and off by default:
+``bias``: q, k and v are W h + b (names ``q_bias``, ``k_bias``, ``v_bias``);
+``qk_norm_span`` = "projection": the RMS norm of q (and of k) runs over the WHOLE projection, all
+heads at once, with a weight of that size, before the heads are split;
+``v_dim``: a value head size other than the key head size (pages hold both at the larger size,
+zero-filled);
+``chunk``: a token sees only the keys of its own chunk of that many positions, counted from
+position 0 of the sequence;
+``sink`` = "zero": one more term exp(0) in the softmax's denominator, with no value;
+``out_gate`` = "sigmoid": the concatenated heads times sigmoid(W_g h), element by element (name
+``gate``), before the output projection;
+``out_scale``: the mixer's result times a constant (applied to the gated heads in 32-bit).
+The first, second, third and sixth take the prologue kernel that knows them
+(``proj_norm_rope_cache``); its rotation is either pair layout of the position part.
 """
 from __future__ import annotations
 
@@ -52,27 +67,64 @@ class GQAAttention:
         pos = spec.get("position") or PartSpec.make("none")
         self.position = position_class(pos)(pos, self.hd, device)
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+        self.vd = int(spec.get("v_dim") or self.hd)
+        self.has_bias = bool(spec.get("bias") or False)
+        self.norm_span = spec.get("qk_norm_span") or "head"
+        self.chunk = int(spec.get("chunk") or 0)
+        self.out_gate = spec.get("out_gate")
+        self.out_scale = float(spec.get("out_scale") if spec.get("out_scale") is not None else 1.0)
+        sink = spec.get("sink")
+        if self.norm_span not in ("head", "projection") or self.out_gate not in (None, "sigmoid") \
+                or sink not in (None, "zero"):
+            raise ConfigError("gqa_attention: qk_norm_span is 'head' or 'projection', out_gate None or "
+                              "'sigmoid', sink None or 'zero'")
+        if self.chunk < 0 or (self.chunk and self.window):
+            raise ConfigError("gqa_attention: a chunk and a window exclude each other")
+        self.sink = torch.zeros(self.nh, dtype=torch.float32, device=device) if sink == "zero" else None
+        self.bias = None
+        # the prologue that knows biases, a norm over the whole projection, unequal head sizes and
+        # a gate's columns beside q, k and v
+        self.wide = bool(self.has_bias or self.vd != self.hd or self.out_gate
+                         or (self.has_qk_norm and self.norm_span == "projection"))
+        if self.wide:
+            if self.shared_kv or (self.has_qk_norm and self.norm_span == "head"):
+                raise ConfigError("gqa_attention: biases, a norm over the projection, a value size of its own "
+                                  "and an output gate go with neither shared_kv nor a per-head norm")
+            if not hasattr(self.position, "table_rotation"):
+                raise ConfigError("gqa_attention: this position part offers no table rotation")
+        self.cache_hd = max(self.hd, self.vd)
 
     # ---- weights -------------------------------------------------------------
     @classmethod
     def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
         n = dict(spec["names"])
+        vd = int(spec.get("v_dim") or spec["head_dim"])
         nq, nk = spec["n_heads"] * spec["head_dim"], spec["n_kv_heads"] * spec["head_dim"]
+        nv, no = spec["n_kv_heads"] * vd, spec["n_heads"] * vd
         shared = bool(spec.get("shared_kv") or False)
-        out = {n["q"]: Expected((nq, hidden_size)), n["o"]: Expected((hidden_size, nq))}
+        out = {n["q"]: Expected((nq, hidden_size)), n["o"]: Expected((hidden_size, no))}
         if not shared:
             out[n["k"]] = Expected((nk, hidden_size))
-            out[n["v"]] = Expected((nk, hidden_size))
+            out[n["v"]] = Expected((nv, hidden_size))
         if spec.get("qk_norm") is not None:
-            out[n["q_norm"]] = Expected((spec["head_dim"],), init="scale")
+            whole = spec.get("qk_norm_span") == "projection"
+            out[n["q_norm"]] = Expected((nq if whole else spec["head_dim"],), init="scale")
             if not shared:
-                out[n["k_norm"]] = Expected((spec["head_dim"],), init="scale")
+                out[n["k_norm"]] = Expected((nk if whole else spec["head_dim"],), init="scale")
+        if spec.get("bias"):
+            out[n["q_bias"]], out[n["k_bias"]], out[n["v_bias"]] = Expected((nq,)), Expected((nk,)), Expected((nv,))
+        if spec.get("out_gate"):
+            out[n["gate"]] = Expected((no, hidden_size))
         return out
 
     def bind(self, tensors: dict) -> None:
         n = self.names
         parts = [tensors[n["q"]]] if self.shared_kv else \
             [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]]
+        if self.out_gate:
+            parts.append(tensors[n["gate"]])          # reads the same input: one product
+        if self.has_bias:
+            self.bias = torch.cat([tensors[n[k]].to(torch.float32) for k in ("q_bias", "k_bias", "v_bias")]).contiguous()
         common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
         self.w_qkv = torch.cat([p.to(common) for p in parts], dim=0).contiguous()
         self.w_o = tensors[n["o"]].contiguous()
@@ -82,7 +134,7 @@ class GQAAttention:
                 self.k_norm_w = tensors[n["k_norm"]].to(torch.float32).contiguous()
 
     def weights(self):
-        return [t for t in (self.w_qkv, self.w_o, self.q_norm_w, self.k_norm_w) if t is not None]
+        return [t for t in (self.w_qkv, self.w_o, self.q_norm_w, self.k_norm_w, self.bias) if t is not None]
 
     def absorb_norm_weight(self, norm) -> bool:
         """Takes the weight of the norm in front of this mixer into the columns of the q/k/v
@@ -99,7 +151,9 @@ class GQAAttention:
         from ..cache.storage import PAGE_SIZE
         return (kernels.product_notices("attention q/k/v", self.w_qkv, self.dtype)
                 + kernels.product_notices("attention output", self.w_o, self.dtype)
-                + kernels.attention_notices("attention", self.hd, PAGE_SIZE, self.dtype))
+                + kernels.attention_notices("attention", self.cache_hd, PAGE_SIZE, self.dtype)
+                + ([f"attention: a chunk of {self.chunk} keys runs on the 32-bit attention kernel"]
+                   if self.chunk and self.dtype == torch.bfloat16 else []))
 
     @property
     def graph_safe(self) -> bool:
@@ -109,26 +163,45 @@ class GQAAttention:
 
     # ---- cache ---------------------------------------------------------------
     def cache_need(self):
-        return None if self.shared_kv else KVNeed(self.nkv, self.hd, self.window)
+        return None if self.shared_kv else KVNeed(self.nkv, self.cache_hd, self.window)
 
     # ---- step ----------------------------------------------------------------
     def forward(self, h: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor) -> None:
-        T = h.shape[0]
-        nk = (0 if self.shared_kv else self.nkv) * self.hd
-        qkv = ctx.workspace.buffer("attn.qkv", (T, self.nh * self.hd + 2 * nk), self.dtype)
+        qkv = ctx.workspace.buffer("attn.qkv", (h.shape[0], self.w_qkv.shape[0]), self.dtype)
         kernels.linear(h, self.w_qkv, qkv)
         self._attend(qkv, ctx, view, residual32)
 
     def forward_from_stream(self, x32: torch.Tensor, norm, ctx, view: KVView,
                             residual32: torch.Tensor) -> None:
         """The same with the block's norm folded into the q/k/v product."""
-        T = x32.shape[0]
-        nk = (0 if self.shared_kv else self.nkv) * self.hd
-        qkv = ctx.workspace.buffer("attn.qkv", (T, self.nh * self.hd + 2 * nk), self.dtype)
+        qkv = ctx.workspace.buffer("attn.qkv", (x32.shape[0], self.w_qkv.shape[0]), self.dtype)
         normed_linear(x32, norm, self.w_qkv, qkv, ctx)
         self._attend(qkv, ctx, view, residual32)
 
+    def _attend_wide(self, qkv: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor) -> None:
+        """q, k, v (and the gate's columns) of one product; the prologue adds the biases, norms all
+        of q and all of k, rotates and writes the pages; attention; gate; output product."""
+        T, ws = qkv.shape[0], ctx.workspace
+        hd, no = self.cache_hd, self.nh * self.vd
+        inv_freq, rot, interleaved = self.position.table_rotation()
+        rope = ctx.rope_table(inv_freq) if inv_freq is not None else None
+        q = ws.buffer("attn.q", (T, self.nh * hd), self.dtype)
+        kernels.proj_norm_rope_cache(qkv, self.bias, self.nh, self.nkv, self.hd, self.vd, self.q_norm_w,
+                                     self.k_norm_w, self.qk_eps, rope, rot, interleaved, ctx, view.pages,
+                                     view.page_size, q)
+        o = ws.buffer("attn.o", (T, self.nh * hd), self.dtype)
+        kernels.attention(q, o, view.pages, ctx, self.nh, self.nkv, hd, view.page_size, self.window,
+                          self.scale, sink=self.sink, chunk=self.chunk)
+        if self.out_gate or hd != self.vd or self.out_scale != 1.0:
+            gate = qkv[:, qkv.shape[1] - no:] if self.out_gate else None
+            og = ws.buffer("attn.gated", (T, no), self.dtype)
+            kernels.gate_mul(o, hd, gate, self.nh, self.vd, self.out_scale, og)
+            o = og
+        kernels.linear(o, self.w_o, residual32, accumulate=True)
+
     def _attend(self, qkv: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor) -> None:
+        if self.wide:
+            return self._attend_wide(qkv, ctx, view, residual32)
         T = qkv.shape[0]
         nq = self.nh * self.hd
         nkv_own = 0 if self.shared_kv else self.nkv        # kv heads this layer projects
@@ -154,7 +227,11 @@ class GQAAttention:
                                     ctx.page_table, view.pages, view.page_size)
         o = ws.buffer("attn.o", (T, nq), self.dtype)
         kernels.attention(q, o, view.pages, ctx, self.nh, self.nkv, self.hd, view.page_size,
-                          self.window, self.scale)
+                          self.window, self.scale, sink=self.sink, chunk=self.chunk)
+        if self.out_scale != 1.0:
+            og = ws.buffer("attn.gated", (T, nq), self.dtype)
+            kernels.gate_mul(o, self.hd, None, self.nh, self.hd, self.out_scale, og)
+            o = og
         kernels.linear(o, self.w_o, residual32, accumulate=True)
 
 

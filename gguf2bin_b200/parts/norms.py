@@ -1,5 +1,8 @@
 """Norms.  ``rmsnorm``: o_j = (w_j * x_j) / sqrt(mean(x^2) + eps), statistics in float32,
-the weight a plain multiplier (src/l3_math.c:21-51 of AnonymoDGH/gguf2bin)."""
+the weight a plain multiplier (src/l3_math.c:21-51 of AnonymoDGH/gguf2bin).  With ``offset`` the
+stored tensor is the weight's distance from that number (a checkpoint that keeps its norm
+weights around zero has ``offset`` 1): the multiplier is ``offset + stored``, added once, in
+32-bit, when the weights are bound."""
 from __future__ import annotations
 
 import torch
@@ -16,14 +19,18 @@ class RMSNorm:
     def __init__(self, spec: PartSpec, width: int, dtype: torch.dtype, device):
         self.eps = float(spec["eps"])
         self.width = int(width)
+        self.offset = float(spec.get("offset") or 0.0)
         self.weight = None
 
     @classmethod
     def expected(cls, spec: PartSpec, width: int, name: str) -> dict:
-        return {name: Expected((int(width),), init="scale")}
+        # a weight stored as a distance from ``offset`` is spread around zero
+        return {name: Expected((int(width),), init="scale" if not spec.get("offset") else "matrix")}
 
     def bind(self, weight: torch.Tensor) -> None:
         self.weight = weight.to(torch.float32).contiguous()      # exact widening
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
 
     def weights(self):
         return (self.weight,) if self.weight is not None else ()

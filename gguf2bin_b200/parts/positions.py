@@ -5,6 +5,9 @@ dimensions of each head, angle = pos * theta^(-2j/r) in float32
 (src/l3_math.c:84-102 of AnonymoDGH/gguf2bin; r = head_dim there).  The frequencies
 are a table handed to the fused norm+rotation kernel, so another encoding that only
 changes the frequencies needs no kernel of its own.
+``rope_interleaved``: the same angles on neighbouring pairs (2j, 2j + 1).  No fused kernel takes
+that layout, so a mixer runs it as a step of its own (``apply``) or hands ``table_rotation()`` to
+a kernel that knows both layouts.
 ``none``: nothing is applied.
 """
 from __future__ import annotations
@@ -36,8 +39,15 @@ class RopeNeox:
             _INV_FREQ[key] = (self.theta ** (-2.0 * j / self.rotary_dim)).to(torch.float32).to(device)
         self.inv_freq = _INV_FREQ[key]
 
+    interleaved = False
+
     def fused_rotation(self):
         return self.inv_freq, self.rotary_dim
+
+    def table_rotation(self):
+        """(inv_freq, rotary_dim, interleaved) for kernels that rotate from the step's (cos, sin)
+        table in either pair layout."""
+        return self.inv_freq, self.rotary_dim, self.interleaved
 
     def apply(self, q, k, ctx) -> None:
         """Rotates q [T, heads*head_dim] and k in place.  The library's own mixer never comes
@@ -56,6 +66,21 @@ class RopeNeox:
             a.copy_(out)
 
 
+class RopeInterleaved(RopeNeox):
+    """Pairs (2j, 2j + 1) of the first ``rotary_dim`` entries of each head."""
+    interleaved = True
+
+    def fused_rotation(self):
+        return None                               # the fused norm + rotation kernel pairs (j, j + r/2)
+
+    def apply(self, q, k, ctx) -> None:
+        from .. import kernels
+        rope = ctx.rope_table(self.inv_freq)
+        for a in (q, k):
+            if a is not None and a.numel():
+                kernels.rotate_heads(a, a.shape[1] // self.head_dim, self.head_dim, rope, self.rotary_dim, True)
+
+
 class NoPosition:
     graph_safe = True          # its step only launches kernels: may be replayed from a CUDA graph
 
@@ -65,9 +90,13 @@ class NoPosition:
     def fused_rotation(self):
         return None, 0                           # fused path with no rotation
 
+    def table_rotation(self):
+        return None, 0, False
+
     def apply(self, q, k, ctx) -> None:
         pass
 
 
 register_position("rope_neox", RopeNeox)
+register_position("rope_interleaved", RopeInterleaved)
 register_position("none", NoPosition)

@@ -1,0 +1,235 @@
+"""Mixers that keep a matrix state per head instead of keys, and a mixer made of several side by side.
+
+``retention``: linear attention with a fixed decay per head and neither softmax nor denominator.
+q = W_q h, k = W_k h (heads x qk_dim), v = W_v h (heads x v_dim); the position part turns q and k;
+k times ``k_scale`` (default qk_dim^-1/2); per head S_t = a_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t;
+each head's o divided by its root mean square (no weight); heads side by side times silu(W_g h);
+output product.
+
+``gated_delta``: the gated delta rule.  q = W_q h, k = W_k h (qk_heads x qk_dim), v = W_v h (heads x
+v_dim); value head i reads query/key head i // (heads / qk_heads).  Each passes a short causal
+convolution over time (``conv_taps`` taps per channel, the last the current token's) and SiLU; q and k
+become unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times qk_dim^-1/2.  Per token and head
+b = sigmoid(W_b h), g = exp(-exp(A_log) softplus(W_a h + dt_bias)); then S <- g S;
+u = b (v - S^T k); S <- S + k u^T; o = S^T q, in this order.  Each head's o divided by its root mean
+square, times a weight over v_dim shared by the heads, times silu(W_g h); output product.
+
+``parallel``: several mixers that read the same input; the result is the sum of theirs, each times
+its ``out_scale``.  A branch is any registered mixer that takes ``out_scale``.
+
+State: S in float32, [slots, heads, v_dim, qk_dim] (a column of S, everything that feeds one output
+channel, is contiguous), and for the convolution a ring of ``conv_taps`` input rows per slot indexed
+by position.  Decays, gates, step sizes, unit norms, rotation and the recurrence are 32-bit; the
+products and the convolution's inputs and outputs are in the compute type.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.storage import StateNeed
+from ..config.specs import ConfigError, PartSpec
+from ..weights.loader import Expected
+from .registry import mixer_class, position_class, register_mixer
+
+
+def _common_dtype(parts):
+    return torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
+
+
+class RetentionMixer:
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.H, self.D, self.V = int(spec["n_heads"]), int(spec["qk_dim"]), int(spec["v_dim"])
+        self.hidden, self.dtype, self.device = int(hidden_size), dtype, device
+        decay = tuple(float(a) for a in spec["decay"])
+        if len(decay) != self.H:
+            raise ConfigError(f"retention: {len(decay)} decays for {self.H} heads")
+        if min(self.H, self.D, self.V) <= 0 or self.D > 512:
+            raise ConfigError("retention: heads, qk_dim (at most 512) and v_dim must be positive")
+        self.decay = torch.tensor(decay, dtype=torch.float32, device=device)
+        k_scale = spec.get("k_scale")
+        self.k_scale = float(k_scale) if k_scale is not None else self.D ** -0.5
+        self.eps = float(spec["eps"])
+        self.out_scale = float(spec.get("out_scale") if spec.get("out_scale") is not None else 1.0)
+        pos = spec.get("position") or PartSpec.make("none")
+        self.position = position_class(pos)(pos, self.D, device)
+        if not hasattr(self.position, "table_rotation"):
+            raise ConfigError("retention: this position part offers no table rotation")
+        self.names = dict(spec["names"])
+        self.w_in = self.w_o = None
+
+    @classmethod
+    def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
+        n = dict(spec["names"])
+        nq, nv = spec["n_heads"] * spec["qk_dim"], spec["n_heads"] * spec["v_dim"]
+        return {n["q"]: Expected((nq, hidden_size)), n["k"]: Expected((nq, hidden_size)),
+                n["v"]: Expected((nv, hidden_size)), n["gate"]: Expected((nv, hidden_size)),
+                n["o"]: Expected((hidden_size, nv))}
+
+    def bind(self, tensors: dict) -> None:
+        n = self.names
+        parts = [tensors[n[k]] for k in ("q", "k", "v", "gate")]
+        common = _common_dtype(parts)
+        self.w_in = torch.cat([p.to(common) for p in parts], dim=0).contiguous()      # one product: q | k | v | gate
+        self.w_o = tensors[n["o"]].contiguous()
+
+    def weights(self):
+        return (self.w_in, self.w_o)
+
+    def notices(self) -> list:
+        return (kernels.product_notices("retention input", self.w_in, self.dtype)
+                + kernels.product_notices("retention output", self.w_o, self.dtype))
+
+    def cache_need(self):
+        return StateNeed((self.H, self.V, self.D), torch.float32)
+
+    def forward(self, h: torch.Tensor, ctx, view, residual32: torch.Tensor) -> None:
+        T, ws = h.shape[0], ctx.workspace
+        nq, nv = self.H * self.D, self.H * self.V
+        proj = ws.buffer("retention.in", (T, 2 * nq + 2 * nv), self.dtype)
+        kernels.linear(h, self.w_in, proj)
+        inv_freq, rot, interleaved = self.position.table_rotation()
+        rope = ctx.rope_table(inv_freq) if inv_freq is not None else None
+        o32 = ws.buffer("retention.o", (T, nv), torch.float32)
+        kernels.state_scan(proj[:, :nq], proj[:, nq:2 * nq], proj[:, 2 * nq:2 * nq + nv], view.states, ctx, o32,
+                           self.H, self.H, self.D, self.V, decay=self.decay, rope=rope, rotary_dim=rot,
+                           interleaved=interleaved, k_scale=self.k_scale)
+        og = ws.buffer("retention.gated", (T, nv), self.dtype)
+        kernels.head_norm_gate(o32, self.H, self.V, None, self.eps, proj[:, 2 * nq + nv:], self.out_scale, og)
+        kernels.linear(og, self.w_o, residual32, accumulate=True)
+
+
+class GatedDeltaMixer:
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.H, self.G = int(spec["n_heads"]), int(spec["n_qk_heads"])
+        self.D, self.V = int(spec["qk_dim"]), int(spec["v_dim"])
+        self.taps = int(spec["conv_taps"])
+        self.hidden, self.dtype, self.device = int(hidden_size), dtype, device
+        if self.G <= 0 or self.H % self.G:
+            raise ConfigError(f"gated_delta: {self.H} heads are not a multiple of {self.G} query/key heads")
+        if min(self.D, self.V) <= 0 or self.D > 512 or not (1 <= self.taps <= 16):
+            raise ConfigError("gated_delta: qk_dim in 1..512, v_dim positive, conv_taps in 1..16")
+        self.eps = float(spec["eps"])
+        self.unit_eps = float(spec.get("unit_eps") if spec.get("unit_eps") is not None else 1e-6)
+        self.out_scale = float(spec.get("out_scale") if spec.get("out_scale") is not None else 1.0)
+        self.names = dict(spec["names"])
+        self.w_in = self.w_ab = self.w_conv = self.w_o = self.a_log = self.dt_bias = self.norm_w = None
+
+    @property
+    def channels(self) -> int:
+        return 2 * self.G * self.D + self.H * self.V
+
+    @classmethod
+    def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
+        n = dict(spec["names"])
+        H, G, D, V, taps = (spec[k] for k in ("n_heads", "n_qk_heads", "qk_dim", "v_dim", "conv_taps"))
+        return {n["q"]: Expected((G * D, hidden_size)), n["k"]: Expected((G * D, hidden_size)),
+                n["v"]: Expected((H * V, hidden_size)), n["gate"]: Expected((H * V, hidden_size)),
+                n["q_conv"]: Expected((G * D, taps)), n["k_conv"]: Expected((G * D, taps)),
+                n["v_conv"]: Expected((H * V, taps)), n["beta"]: Expected((H, hidden_size)),
+                n["a"]: Expected((H, hidden_size)), n["a_log"]: Expected((H,)), n["dt_bias"]: Expected((H,)),
+                n["norm"]: Expected((V,), init="scale"), n["o"]: Expected((hidden_size, H * V))}
+
+    def bind(self, tensors: dict) -> None:
+        n = self.names
+        parts = [tensors[n[k]] for k in ("q", "k", "v", "gate")]
+        common = _common_dtype(parts)
+        self.w_in = torch.cat([p.to(common) for p in parts], dim=0).contiguous()       # q | k | v | gate
+        ab = [tensors[n["a"]], tensors[n["beta"]]]
+        self.w_ab = torch.cat([p.to(_common_dtype(ab)) for p in ab], dim=0).contiguous()       # decay input | write strength
+        conv = torch.cat([tensors[n[k]].to(torch.float32) for k in ("q_conv", "k_conv", "v_conv")], dim=0)
+        self.w_conv = conv.t().contiguous()               # [taps, channels]: a tap's weights side by side
+        self.a_log = tensors[n["a_log"]].to(torch.float32).contiguous()
+        self.dt_bias = tensors[n["dt_bias"]].to(torch.float32).contiguous()
+        self.norm_w = tensors[n["norm"]].to(torch.float32).contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+
+    def weights(self):
+        return (self.w_in, self.w_ab, self.w_conv, self.a_log, self.dt_bias, self.norm_w, self.w_o)
+
+    def notices(self) -> list:
+        return (kernels.product_notices("gated delta input", self.w_in, self.dtype)
+                + kernels.product_notices("gated delta output", self.w_o, self.dtype))
+
+    def cache_need(self):
+        need = {"state": StateNeed((self.H, self.V, self.D), torch.float32)}
+        if self.taps > 1:
+            need["conv"] = StateNeed((self.taps, self.channels), self.dtype, by_position=True)
+        return need
+
+    def forward(self, h: torch.Tensor, ctx, view, residual32: torch.Tensor) -> None:
+        T, ws = h.shape[0], ctx.workspace
+        C, nq, nv = self.channels, self.G * self.D, self.H * self.V
+        proj = ws.buffer("delta.in", (T, C + nv), self.dtype)
+        kernels.linear(h, self.w_in, proj)
+        ab = ws.buffer("delta.ab", (T, 2 * self.H), torch.float32)
+        kernels.linear(h, self.w_ab, ab)
+        mixed = ws.buffer("delta.conv", (T, C), self.dtype)
+        ring = view["conv"].states if self.taps > 1 else None
+        kernels.short_conv(proj[:, :C], self.w_conv, ring, ctx, mixed, act=True)
+        o32 = ws.buffer("delta.o", (T, nv), torch.float32)
+        kernels.state_scan(mixed[:, :nq], mixed[:, nq:2 * nq], mixed[:, 2 * nq:], view["state"].states, ctx, o32,
+                           self.H, self.G, self.D, self.V, ab=ab, a_log=self.a_log, dt_bias=self.dt_bias,
+                           q_scale=self.D ** -0.5, unit_eps=self.unit_eps)
+        og = ws.buffer("delta.gated", (T, nv), self.dtype)
+        kernels.head_norm_gate(o32, self.H, self.V, self.norm_w, self.eps, proj[:, C:], self.out_scale, og)
+        kernels.linear(og, self.w_o, residual32, accumulate=True)
+
+
+class ParallelMixer:
+    """Branches side by side on one input; what each stores is kept under ``<branch>.<name>``."""
+
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
+        branches = spec["branches"]                       # ((name, PartSpec), ...)
+        if not branches:
+            raise ConfigError("parallel: at least one branch")
+        self.branches = [(name, mixer_class(s)(s, hidden_size, dtype, device)) for name, s in branches]
+
+    @classmethod
+    def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
+        out = {}
+        for _, s in spec["branches"]:
+            out.update(mixer_class(s).expected(s, hidden_size))
+        return out
+
+    def bind(self, tensors: dict) -> None:
+        for _, m in self.branches:
+            m.bind(tensors)
+
+    def weights(self):
+        for _, m in self.branches:
+            yield from getattr(m, "weights", tuple)()
+
+    def notices(self) -> list:
+        return [line for _, m in self.branches for line in getattr(m, "notices", list)()]
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(m, "graph_safe", False) for _, m in self.branches)
+
+    def cache_need(self):
+        need = {}
+        for name, m in self.branches:
+            one = m.cache_need()
+            if isinstance(one, dict):
+                need.update({f"{name}.{k}": v for k, v in one.items() if v is not None})
+            elif one is not None:
+                need[name] = one
+        return need or None
+
+    def forward(self, h: torch.Tensor, ctx, view, residual32: torch.Tensor) -> None:
+        view = view or {}
+        for name, m in self.branches:
+            own = view.get(name)
+            if own is None:
+                own = {k[len(name) + 1:]: v for k, v in view.items() if k.startswith(name + ".")} or None
+            m.forward(h, ctx, own, residual32)
+
+
+register_mixer("retention", RetentionMixer)
+register_mixer("gated_delta", GatedDeltaMixer)
+register_mixer("parallel", ParallelMixer)
