@@ -171,7 +171,9 @@ def delta_rule(h, W, pre, m, eps, state=None):
 
 
 # ---- routed feed-forward -------------------------------------------------------------------------
-def routed_ff(h, W, pre, mlp):
+def routed_ff(h, W, pre, mlp, margins=None):
+    """``margins``: a list that receives, per token, how far the last chosen expert's choice score
+    lies above the best one not chosen (a test that compares with a 16-bit run wants that clear)."""
     r = mlp["router"]
     E, I, top = r["experts"], r["identity"], r["top"]
     z = h @ W[pre + "router"].T                                   # [T, E + I]
@@ -180,7 +182,10 @@ def routed_ff(h, W, pre, mlp):
     pick = s + W[pre + "correction"]
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
-        for e in np.argsort(-pick[t], kind="stable")[:top]:
+        order = np.argsort(-pick[t], kind="stable")
+        if margins is not None and top < E + I:
+            margins.append(pick[t, order[top - 1]] - pick[t, order[top]])
+        for e in order[:top]:
             if e >= E:
                 y = h[t]
             else:
@@ -200,7 +205,13 @@ class Plain:
         self.state = [None] * len(cfg["layers"])
         self.n = 0
 
-    def forward(self, tokens, layers_out=None):
+    def snapshot(self):
+        return list(self.state), self.n
+
+    def restore(self, snap) -> None:
+        self.state, self.n = list(snap[0]), snap[1]
+
+    def forward(self, tokens, layers_out=None, margins=None):
         """Logits [T, vocab] of these tokens, which follow the ones given before."""
         cfg, W, eps = self.cfg, self.W, self.eps
         x = W["embed"][np.asarray(tokens)]
@@ -219,12 +230,13 @@ class Plain:
                 raise ValueError(layer["type"])
             x = x + offset_norm(y, W[f"l{i}.norm1"], eps)
             if layer.get("mlp") is not None:
-                x = x + offset_norm(routed_ff(x, W, f"l{i}.mlp.", layer["mlp"]), W[f"l{i}.norm2"], eps)
-            if layer_out_wanted(layers_out):
+                x = x + offset_norm(routed_ff(x, W, f"l{i}.mlp.", layer["mlp"], margins), W[f"l{i}.norm2"], eps)
+            if layers_out is not None:
                 layers_out.append(x.copy())
         self.n += len(tokens)
         return offset_norm(x, W["final.norm"], eps) @ W["embed"].T
 
 
-def layer_out_wanted(layers_out) -> bool:
-    return layers_out is not None
+def forward(cfg: dict, W: dict, tokens) -> np.ndarray:
+    """Logits of every position of one sequence."""
+    return Plain(cfg, W).forward(list(tokens))
