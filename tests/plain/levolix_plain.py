@@ -173,7 +173,8 @@ def delta_rule(h, W, pre, m, eps, state=None):
 # ---- routed feed-forward -------------------------------------------------------------------------
 def routed_ff(h, W, pre, mlp, margins=None):
     """``margins``: a list that receives, per token, how far the last chosen expert's choice score
-    lies above the best one not chosen (a test that compares with a 16-bit run wants that clear)."""
+    lies above the best one not chosen, as a fraction of the larger of the two experts' scores (a
+    test that compares with a 16-bit run wants that clear)."""
     r = mlp["router"]
     E, I, top = r["experts"], r["identity"], r["top"]
     z = h @ W[pre + "router"].T                                   # [T, E + I]
@@ -184,7 +185,8 @@ def routed_ff(h, W, pre, mlp, margins=None):
     for t in range(h.shape[0]):
         order = np.argsort(-pick[t], kind="stable")
         if margins is not None and top < E + I:
-            margins.append(pick[t, order[top - 1]] - pick[t, order[top]])
+            a, b = order[top - 1], order[top]
+            margins.append((pick[t, a] - pick[t, b]) / max(s[t, a], s[t, b]))
         for e in order[:top]:
             if e >= E:
                 y = h[t]
