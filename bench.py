@@ -2,7 +2,7 @@
 """Decode and prefill throughput of gguf2bin_b200 on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode|ragged8|b64|senotar] [--batch B] [--layers L] [--context C]
+                    [--workload decode|ragged8|b64|senotar|levolix] [--batch B] [--layers L] [--context C]
                     [--no-points] [--sizes 0.6b|8b|14b]
 
 The default run has the layer sizes of Qwen3-0.6B (28 layers, width 1024, 16/8 heads of
@@ -41,6 +41,11 @@ same width, layer count, vocabulary and (within 3 %) parameter count, and times 
 prompt step of 2,048 tokens and decode steps at batch 8 behind 2,048-token prompts, on the
 device, with the fraction of the tensor-core peak (prompt) and of the copy bandwidth (decode)
 that each reaches.  It prints one JSON line of its own shape.
+
+``--workload levolix`` is the same kind of comparison for Levolix (retention layers and layers with
+chunked attention beside the gated delta rule, routed experts): active parameters per token within
+a few per cent of the Qwen3 model's; the decode roofline counts every expert matrix once, the
+states read and written, and the keys and values of a request's current chunk.
 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the
 fallback figures 6.65 TB/s and 1.59 PFLOP/s.  Inputs are synthetic.  Between timed steps
@@ -333,12 +338,126 @@ def senotar_comparison(a, pk) -> int:
     return 0
 
 
+# ---- Levolix beside Qwen3 at equal sizes ----------------------------------------------------------
+# name: (width, retention heads / key size / value size, attention heads / kv heads / head size / chunk,
+#        delta-rule heads / query-key heads / key size / value size, experts / identity / top / expert ff;
+#        Qwen3's heads, kv heads, head size, ff)
+LEVOLIX_SIZES = {
+    "w1024": (1024, (4, 128, 256), (8, 4, 128, 512), (4, 2, 128, 128), (16, 2, 4, 768), 16, 8, 128, 3072),
+    "w2048": (2048, (8, 128, 256), (16, 8, 128, 512), (8, 4, 128, 128), (16, 2, 4, 1536), 16, 8, 128, 6144),
+    "w4096": (4096, (16, 128, 256), (32, 8, 128, 512), (16, 4, 128, 128), (16, 2, 4, 3072), 32, 8, 128, 12288),
+}
+
+
+def levolix_config(width, ret, att, delta, moe, layers, vocab) -> dict:
+    """Two retention layers, then one with attention and the delta rule side by side, and so on."""
+    out = []
+    mlp = dict(kind="moe", expert=dict(ff=moe[3]), router=dict(experts=moe[0], identity=moe[1], top=moe[2]))
+    for i in range(layers):
+        if i % 3 < 2:
+            H, D, V = ret
+            decay = [1.0 - 2.0 ** (-5 - 6.0 * h / max(1, H - 1)) for h in range(H)]
+            out.append(dict(type="retention", mlp=mlp,
+                            mixer=dict(heads=H, dim=D, vdim=V, decay=decay, rot=dict(dims=D, base=1e6))))
+        else:
+            H, G, D, chunk = att
+            left = dict(heads=H, kv_heads=G, dim=D, vdim=D, mask=dict(size=chunk), rot=dict(dims=D, base=5e4), scale=D ** -0.5)
+            right = dict(heads=delta[0], kv_heads=delta[1], dim=delta[2], vdim=delta[3], conv=4)
+            out.append(dict(type="parallel", mlp=mlp, mixer=dict(left=left, right=right, left_scale=1.0, right_scale=1.0)))
+    return dict(architecture="Levolix", width=width, vocab=vocab, norm=dict(eps=1e-6), layers=out)
+
+
+def levolix_bytes_and_flops(cfg: dict) -> dict:
+    """Parameters a token's step multiplies by (the chosen experts only), the bytes a decode step of a
+    batch reads at least (every matrix once: a batch of 8 with 4 choices each touches most experts),
+    and what every live request adds (keys and values of its chunk, its states)."""
+    W, V = cfg["width"], cfg["vocab"]
+    active = total = state_bytes = kv_per_token = attn = 0
+    for layer in cfg["layers"]:
+        m, mlp = layer["mixer"], layer["mlp"]
+        if layer["type"] == "retention":
+            mix = W * m["heads"] * (2 * m["dim"] + 3 * m["vdim"])
+            state_bytes += 2 * 4 * m["heads"] * m["dim"] * m["vdim"]                 # read and written
+        else:
+            l, r = m["left"], m["right"]
+            mix = W * (2 * l["heads"] * l["dim"] + 2 * l["kv_heads"] * l["dim"] + 2 * l["heads"] * l["vdim"])
+            mix += W * (2 * r["kv_heads"] * r["dim"] + 3 * r["heads"] * r["vdim"] + 2 * r["heads"])
+            state_bytes += 2 * 4 * r["heads"] * r["dim"] * r["vdim"]
+            kv_per_token += 2 * 2 * l["kv_heads"] * l["dim"]
+            attn += 4 * l["heads"] * l["dim"]
+        e = mlp["router"]
+        one = 3 * W * mlp["expert"]["ff"]
+        real_share = e["experts"] / (e["experts"] + e["identity"])
+        active += mix + W * (e["experts"] + e["identity"]) + one * e["top"] * real_share
+        total += mix + W * (e["experts"] + e["identity"]) + one * e["experts"]
+    return dict(layer_params=active, total_params=total, weight_bytes=2 * (total + V * W), state_bytes=state_bytes,
+                kv_bytes_per_token=kv_per_token, attn_flops_per_pair=attn)
+
+
+def levolix_comparison(a, pk) -> int:
+    import torch
+    from gguf2bin_b200.api import LLM
+    layers, vocab, batch, T = a.layers or 6, 151936, a.batch or 8, a.prefill_tokens
+    steps, warmup = a.steps or 128, max(a.warmup, 8)
+    max_tokens = batch * (T + warmup + steps + 128)
+    rows = {}
+    clocks = ClockSampler()
+    clocks.start()
+    for name, (width, ret, att, delta, moe, q_heads, q_kv, q_hd, q_ff) in LEVOLIX_SIZES.items():
+        if a.sizes_only and name not in a.sizes_only.split(","):
+            continue
+        row = {}
+        for arch in ("levolix", "qwen3"):
+            if arch == "levolix":
+                cfg = levolix_config(width, ret, att, delta, moe, layers, vocab)
+                sizes = levolix_bytes_and_flops(cfg)
+                chunk = att[3]
+                pairs = sum(min(t % chunk, t) + 1 for t in range(T))        # keys a token sees: its chunk only
+                flops = 2.0 * T * sizes["layer_params"] + sizes["attn_flops_per_pair"] * pairs + 2.0 * vocab * width
+                extra = batch * sizes["state_bytes"]
+                ctx_cap = chunk / 2.0
+            else:
+                cfg = dict(QWEN3_0P6B, hidden_size=width, intermediate_size=q_ff, num_hidden_layers=layers,
+                           num_attention_heads=q_heads, num_key_value_heads=q_kv, head_dim=q_hd, vocab_size=vocab,
+                           tie_word_embeddings=True)
+                sizes = model_bytes_and_flops(cfg, layers)
+                sizes["weight_bytes"] -= 2 * vocab * width               # tied: the table is the head
+                sizes["layer_params"] *= layers
+                flops = prefill_flops(cfg, layers, [T])
+                extra, ctx_cap = 0, None
+            llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seqs=batch + 1)
+            first, ms, plain = timed_prompt_step(llm, random_prompts(1, T, vocab, 1), repeats=3)
+            sec, per_step, mean_ctx = decode_device_timed(llm, random_prompts(batch, T, vocab, 100), steps, warmup,
+                                                          vocab, whole_batch_prefill=False)
+            step_bytes = sizes["weight_bytes"] + extra + batch * (min(mean_ctx, ctx_cap) if ctx_cap else mean_ctx) \
+                * sizes["kv_bytes_per_token"]
+            gbs = step_bytes / (sec / steps) / 1e9
+            row[arch] = dict(
+                active_parameters_per_layer_m=round(sizes["layer_params"] / layers / 1e6, 1),
+                prefill_tokens_per_s=round(T / (ms / 1e3)), prefill_ms=round(ms, 3), prefill_plain_ms=round(plain, 3),
+                prefill_frac_of_tensor_peak=round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+                decode_tokens_per_s=round(batch * steps / sec), decode_ms_per_step=round(sec / steps * 1e3, 4),
+                decode_launches_per_step=per_step, decode_step_mb=round(step_bytes / 1e6, 1), decode_gbs=round(gbs),
+                decode_frac_of_copy_bandwidth=round(gbs / pk["hbm_gbs"], 3))
+            del llm
+            torch.cuda.empty_cache()
+        rows[name] = row
+    print(json.dumps({"metric": "prefill and decode tokens/s of Levolix beside Qwen3 at equal sizes (random weights)",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+                      "config": {"layers": layers, "vocab": vocab, "prompt_tokens": T, "decode_batch": batch,
+                                 "decode_context_from": T + warmup, "decode_steps": steps, "peaks": pk["source"],
+                                 "l2": "inputs larger than L2 (weights, states and cache read every step)"},
+                      "sizes": rows, "clocks": clocks.stop()}))
+    return 0
+
+
 WORKLOADS = {
     # name: (sizes, batch, what it is)
     "decode": ("0.6b", 8, "every sequence prefilled to half the context, then decoded"),
     "ragged8": ("8b", 8, "8 prompts with lengths uniform in [128, 2048] in ONE prompt step, then 256 decode steps"),
     "b64": ("14b", 64, "64 prompts of 512 tokens in one prompt step, decoded to a context of 2048"),
     "senotar": (None, 8, "Senotar beside Qwen3 at equal sizes: a 2,048-token prompt step and batch-8 decode steps each"),
+    "levolix": (None, 8, "Levolix beside Qwen3 at equal sizes: a 2,048-token prompt step and batch-8 decode steps each"),
 }
 
 
@@ -359,7 +478,7 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the prompt of the prefill figure (decode workload; default 2048)")
     ap.add_argument("--sizes-only", default=None,
-                    help="senotar workload: a comma-separated subset of " + ",".join(EQUAL_SIZES))
+                    help="senotar and levolix workloads: a comma-separated subset of " + ",".join(EQUAL_SIZES))
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -375,6 +494,8 @@ def main() -> int:
         a.warmup = 3
     if a.workload == "senotar":
         return senotar_comparison(a, peaks())
+    if a.workload == "levolix":
+        return levolix_comparison(a, peaks())
 
     import numpy as np
     import torch

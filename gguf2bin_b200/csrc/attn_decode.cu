@@ -1,7 +1,8 @@
 // Decode attention over the paged bfloat16 cache, split along the keys.
 //
 // One token per query row: every token t of the step attends, for each of its query
-// heads, to the keys 0..pos_t of its own sequence (optionally only the last `window`).
+// heads, to the keys 0..pos_t of its own sequence (optionally only the last `window`, or, with a
+// negative `window`, only those of the token's own chunk of -window positions).
 // Grid (key chunk, kv head x head tile, token): a CTA takes one chunk of CHUNK_KEYS keys
 // (chunks start at absolute positions that are multiples of CHUNK_KEYS, so the split of
 // a token's keys depends on nothing but its position) and ALL query heads that share the
@@ -274,7 +275,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
   // large while a take-back is still on its way, which the "- 1" allows for.  Not with a
   // window, whose lower edge moves with the position.
   const int hint = ld_volatile(tok_pos + t);
-  const bool early = window <= 0 && (first_page + warp + 1) * PAGE <= hint - 1;
+  const bool early = window == 0 && (first_page + warp + 1) * PAGE <= hint - 1;
   if (early) {
     load_panel(k_smem, panel_of(first_page + warp, 0), lane);
     cp_async_commit();
@@ -283,7 +284,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
   }
   pdl_wait();
   const int pos = ld_volatile(tok_pos + t);
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = first_visible_key(pos, window);
   if (key_begin > pos || key_begin + CHUNK_KEYS <= lo) return;     // no key of this chunk is seen (then nothing was fetched early)
 
   // the pages of this warp: key_begin/PAGE + warp, + WARPS, ... that hold a visible key (the
@@ -345,7 +346,7 @@ attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__
   const int t = (int)(th / nh);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = tok_pos[t];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = first_visible_key(pos, window);
   const int c0 = lo / CHUNK_KEYS, c1 = pos / CHUNK_KEYS;
   const float2 *ml = part_ml + th * n_chunks;
   float M = -INFINITY;

@@ -178,7 +178,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int4 tile = tiles[item / nh];
   const int b = tile.x, t0 = tile.y, n_rows = tile.z, pos0 = tile.w;
   const int h = item % nh, kvh = h / (nh / nkv);
-  const int first_page = window > 0 ? max(0, pos0 - window + 1) / PAGE : 0;
+  const int first_page = first_visible_key(pos0, window) / PAGE;
   const int last_page = (pos0 + n_rows - 1) / PAGE;
   const int n_pages = last_page - first_page + 1;
 
@@ -288,8 +288,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int row0 = (warp & 3) * 32 + (warp >> 2) * 16;
     const int rA = row0 + g, rB = rA + 8;
     const int pos_a = pos0 + rA, pos_b = pos0 + rB;
-    const int lo_a = window > 0 ? max(0, pos_a - window + 1) : 0;
-    const int lo_b = window > 0 ? max(0, pos_b - window + 1) : 0;
+    const int lo_a = first_visible_key(pos_a, window);
+    const int lo_b = first_visible_key(pos_b, window);
     const uint32_t lane_base = tmem + ((uint32_t)row0 << 16);
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;      // l: this thread's keys only
     bool ok = true;
@@ -317,7 +317,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       // Only pages that cross the limits of the warp's rows are masked (warp-uniform test).
       const int warp_pos_min = pos0 + row0, warp_pos_max = warp_pos_min + 15;
       const bool partial = key0 + PAGE - 1 > warp_pos_min ||
-                           (window > 0 && key0 < max(0, warp_pos_max - window + 1));
+                           (window != 0 && key0 < first_visible_key(warp_pos_max, window));
       if (partial) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)

@@ -191,7 +191,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int4 tile = tiles[item / nh];
   const int b = tile.x, t0 = tile.y, n_rows = tile.z, pos0 = tile.w;
   const int h = item % nh, kvh = h / (nh / nkv);
-  const int first_page = window > 0 ? max(0, pos0 - window + 1) / PAGE : 0;
+  const int first_page = first_visible_key(pos0, window) / PAGE;
   const int last_page = (pos0 + n_rows - 1) / PAGE;
   const int n_pages = last_page - first_page + 1;
 
@@ -300,7 +300,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int g = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
     const int pos = pos0 + row;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = first_visible_key(pos, window);
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t o_base = lane_base + O_COL0 + O_COLS * g;
     float m = -INFINITY, l = 0.f;
@@ -330,7 +330,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       // Only pages that cross the limits of the warp's rows are masked (warp-uniform test).
       const int warp_pos_min = pos0 + (warp & 3) * 32, warp_pos_max = warp_pos_min + 31;
       const bool partial = key0 + PAGE - 1 > warp_pos_min ||
-                           (window > 0 && key0 < max(0, warp_pos_max - window + 1));
+                           (window != 0 && key0 < first_visible_key(warp_pos_max, window));
       if (partial) {
 #pragma unroll
         for (int j = 0; j < 64; ++j)

@@ -102,6 +102,16 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// ---- which keys a token sees -------------------------------------------------
+// The lowest key position that the token at `pos` attends to.  `window` > 0: the last `window`
+// keys; `window` < 0: the keys of the token's own chunk of -window positions (chunks count from
+// position 0 of the sequence); 0: every key.  Never decreases as `pos` grows.
+__device__ __forceinline__ int first_visible_key(int pos, int window) {
+  if (window > 0) return max(0, pos - window + 1);
+  if (window < 0) return (pos / -window) * -window;
+  return 0;
+}
+
 // ---- reductions ------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -465,9 +465,9 @@ def attention(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size
               scale, sink=None, planes: int = 2, gate=None, chunk: int = 0) -> None:
     """Attention of a step: the tensor-core kernels when they take the case, else the
     32-bit kernel.  ``q`` and ``gate`` may be column ranges of a wider buffer."""
-    if q.dtype == torch.bfloat16 and not chunk:
+    if q.dtype == torch.bfloat16:
         if (_bf16 or _bf16_mod()).attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim,
-                                       page_size, window, scale, sink, planes, gate):
+                                       page_size, window, scale, sink, planes, gate, chunk):
             return
     attn_generic(q, out, cache_pages, ctx.tok_pos, ctx.tok_seq, ctx.page_table, n_heads,
                  n_kv_heads, head_dim, page_size, window, scale, sink, planes, gate, chunk)

@@ -283,7 +283,12 @@ def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, bl
 
 
 def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                   scale, sink=None, planes: int = 2, gate=None) -> bool:
+                   scale, sink=None, planes: int = 2, gate=None, chunk: int = 0) -> bool:
+    """``chunk`` > 0 (keys of the token's own chunk only) reaches the kernels as a negative window."""
+    if chunk:
+        if window:
+            return False
+        window = -int(chunk)
     if head_dim not in FAST_HEAD_SIZES or page_size != 64 or cache_pages.dtype != torch.bfloat16:
         return False
     if q.stride(1) != 1 or q.stride(0) % 8 or q.data_ptr() % 16 or not out.is_contiguous():
@@ -300,7 +305,7 @@ def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page
         attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale,
                         sink=sink, planes=planes, gate=gate)
         return True
-    if sink is not None or planes != 2 or gate is not None or q.stride(0) != n_heads * head_dim:
+    if sink is not None or planes != 2 or gate is not None or q.stride(0) != n_heads * head_dim or window < 0:
         # the mma.sync prompt kernel knows none of these
         return False
     if getattr(ctx, "attn_tiles", None) is not None and ctx.n_attn_tiles > 0:

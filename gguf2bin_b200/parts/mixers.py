@@ -151,9 +151,7 @@ class GQAAttention:
         from ..cache.storage import PAGE_SIZE
         return (kernels.product_notices("attention q/k/v", self.w_qkv, self.dtype)
                 + kernels.product_notices("attention output", self.w_o, self.dtype)
-                + kernels.attention_notices("attention", self.cache_hd, PAGE_SIZE, self.dtype)
-                + ([f"attention: a chunk of {self.chunk} keys runs on the 32-bit attention kernel"]
-                   if self.chunk and self.dtype == torch.bfloat16 else []))
+                + kernels.attention_notices("attention", self.cache_hd, PAGE_SIZE, self.dtype))
 
     @property
     def graph_safe(self) -> bool:
