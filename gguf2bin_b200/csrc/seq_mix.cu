@@ -438,6 +438,284 @@ extern "C" int g2b_state_scan(int mode, int dtype, const void *q, int q_stride, 
 }
 
 // ---------------------------------------------------------------------------
+// the state scan for prompts: q and k prepared once by a kernel of their own, then a scan whose
+// next tile of tokens is on its way into shared memory while the current one is computed
+// ---------------------------------------------------------------------------
+// scan_prep: one warp per (token, query/key head): rotation or unit norm, scales; float out.
+template <typename T>
+__global__ void __launch_bounds__(128)
+scan_prep_kernel(const T *__restrict__ q, int q_stride, const T *__restrict__ k, int k_stride, int n_tokens, int G, int D,
+                 const float2 *__restrict__ rope, int rot, int interleaved, float q_scale, float k_scale,
+                 int unit_norm, float unit_eps, float *__restrict__ qf, float *__restrict__ kf) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float sq[4][SCAN_MAX_D];
+  __shared__ float sk[4][SCAN_MAX_D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * 4 + warp;
+  if (item >= (long long)n_tokens * G) return;
+  const int t = (int)(item / G), g = (int)(item % G);
+  const T *qp = q + (size_t)t * q_stride + (size_t)g * D;
+  const T *kp = k + (size_t)t * k_stride + (size_t)g * D;
+  float nq = 0.f, nk = 0.f;
+  for (int j = lane; j < D; j += 32) {
+    const float x = to_f32(qp[j]), y = to_f32(kp[j]);
+    sq[warp][j] = x;
+    sk[warp][j] = y;
+    nq = fmaf(x, x, nq);
+    nk = fmaf(y, y, nk);
+  }
+  __syncwarp();
+  float fq = q_scale, fk = k_scale;
+  if (unit_norm) {
+    fq *= 1.f / sqrtf(warp_sum(nq) + unit_eps);
+    fk *= 1.f / sqrtf(warp_sum(nk) + unit_eps);
+  }
+  if (rope) {
+    const float2 *cs = rope + (size_t)t * (rot >> 1);
+    rotate_in_place(sq[warp], cs, rot, interleaved, lane);
+    rotate_in_place(sk[warp], cs, rot, interleaved, lane);
+    __syncwarp();
+  }
+  for (int j = lane; j < D; j += 32) {
+    qf[((size_t)t * G + g) * D + j] = sq[warp][j] * fq;
+    kf[((size_t)t * G + g) * D + j] = sk[warp][j] * fk;
+  }
+}
+
+__device__ __forceinline__ void cp_async_f4(float *smem, const float *g) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(addr), "l"(g));
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+// 128 threads; a column of the state is held by L lanes, lane l the rows 4 (j L + l) .. + 3, j < 4
+// (16 L >= D; rows from D on are zeros).  Shared memory: two buffers of `tile` tokens of q and k
+// (rows of Dp = D rounded up to 4 L floats), of the columns' v, and of the tokens' two gates.
+#define PSCAN_THREADS 128
+struct PScanArgs {
+  const float *qf, *kf;       // [T, G, D] prepared
+  const void *v;              // compute type, rows of a wider buffer
+  int v_stride, H, G, D, V;
+  const float *decay, *ab, *A_log, *dt_bias;
+  float *state;               // [slots, H, V, D]
+  const int *seq_meta;
+  float *out;                 // [T, H*V]
+  int L, Dp, tile;
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(PSCAN_THREADS)
+state_scan_prompt_kernel(const PScanArgs a) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ __align__(16) float psm[];
+  const int D = a.D, V = a.V, H = a.H, L = a.L, Dp = a.Dp, TT = a.tile;
+  const int cols = PSCAN_THREADS / L;
+  float *bq[2], *bk[2], *bv[2], *bg[2], *bb[2];
+  {
+    float *p = psm;
+    for (int i = 0; i < 2; ++i) { bq[i] = p; p += TT * Dp; bk[i] = p; p += TT * Dp; }
+    for (int i = 0; i < 2; ++i) { bv[i] = p; p += TT * cols; bg[i] = p; p += TT; bb[i] = p; p += TT; }
+  }
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qk_head = h / (H / a.G);
+  const int lane_in_col = threadIdx.x % L, col_local = threadIdx.x / L;
+  const int c = blockIdx.x * cols + col_local;
+  const bool live = c < V;
+  const int first_row = a.seq_meta[4 * b + 0], n = a.seq_meta[4 * b + 1], slot = a.seq_meta[4 * b + 3];
+  const int RG = Dp / (4 * L);                     // groups of four rows per lane, at most 4
+  float *sp = a.state + (((size_t)slot * H + h) * V + (live ? c : 0)) * D;
+  const bool vec = (D & 3) == 0;
+  float S[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int d = 4 * (j * L + lane_in_col) + i;
+      S[j][i] = (live && j < RG && d < D) ? sp[d] : 0.f;
+    }
+  float decay = 1.f, A = 0.f, dt = 0.f;
+  if (MODE == 0) decay = a.decay[h];
+  else { A = expf(a.A_log[h]); dt = a.dt_bias[h]; }
+  const T *vg = (const T *)a.v;
+  // rows from D on stay zero in both buffers
+  for (int i = threadIdx.x; i < 4 * TT * Dp; i += PSCAN_THREADS) psm[i] = 0.f;
+  __syncthreads();
+
+  auto fetch_qk = [&](int t0, int nt, int buf) {
+    const float *qsrc = a.qf + ((size_t)(first_row + t0) * a.G + qk_head) * D;
+    const float *ksrc = a.kf + ((size_t)(first_row + t0) * a.G + qk_head) * D;
+    const size_t row = (size_t)a.G * D;
+    if (vec) {
+      const int per = D >> 2;
+      for (int i = threadIdx.x; i < nt * per; i += PSCAN_THREADS) {
+        const int tt = i / per, p = i % per;
+        cp_async_f4(bq[buf] + tt * Dp + 4 * p, qsrc + tt * row + 4 * p);
+        cp_async_f4(bk[buf] + tt * Dp + 4 * p, ksrc + tt * row + 4 * p);
+      }
+    } else {
+      for (int i = threadIdx.x; i < nt * D; i += PSCAN_THREADS) {
+        const int tt = i / D, p = i % D;
+        bq[buf][tt * Dp + p] = qsrc[tt * row + p];
+        bk[buf][tt * Dp + p] = ksrc[tt * row + p];
+      }
+    }
+    cp_async_commit_group();
+  };
+  // the small per-token values go through registers: loaded before the tile in work is computed,
+  // stored behind it
+  float rv[4] = {0.f, 0.f, 0.f, 0.f}, rg = 0.f, rb = 0.f;          // TT * cols <= 4 * 128
+  auto load_small = [&](int t0, int nt) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = threadIdx.x + u * PSCAN_THREADS;
+      const int tt = i / cols, cc = i % cols, col = blockIdx.x * cols + cc;
+      rv[u] = (tt < nt && col < V) ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * V + col]) : 0.f;
+    }
+    if (MODE == 1 && threadIdx.x < nt) {
+      const size_t row = (size_t)(first_row + t0 + threadIdx.x) * 2 * H;
+      rg = a.ab[row + h];
+      rb = a.ab[row + H + h];
+    }
+  };
+  auto store_small = [&](int nt, int buf) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = threadIdx.x + u * PSCAN_THREADS;
+      if (i < TT * cols) bv[buf][i] = rv[u];
+    }
+    if (MODE == 1 && threadIdx.x < nt) {
+      bg[buf][threadIdx.x] = expf(-A * softplus_f(rg + dt));
+      bb[buf][threadIdx.x] = sigmoid_f(rb);
+    }
+  };
+
+  fetch_qk(0, min(TT, n), 0);
+  load_small(0, min(TT, n));
+  store_small(min(TT, n), 0);
+  int buf = 0;
+  for (int t0 = 0; t0 < n; t0 += TT, buf ^= 1) {
+    const int nt = min(TT, n - t0);
+    const int next = t0 + TT, nn = min(TT, n - next);
+    cp_async_wait_all();
+    __syncthreads();                               // tile t0 is in `buf`; nobody reads buf ^ 1 any more
+    if (next < n) {
+      fetch_qk(next, nn, buf ^ 1);
+      load_small(next, nn);
+    }
+    const float *tq = bq[buf], *tk = bk[buf];
+    for (int tt = 0; tt < nt; ++tt) {
+      const float v = bv[buf][tt * cols + col_local];
+      float o = 0.f;
+      if (MODE == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < RG) {
+            const float4 kd = *(const float4 *)(tk + tt * Dp + 4 * (j * L + lane_in_col));
+            const float4 qd = *(const float4 *)(tq + tt * Dp + 4 * (j * L + lane_in_col));
+            S[j][0] = fmaf(decay, S[j][0], kd.x * v);
+            S[j][1] = fmaf(decay, S[j][1], kd.y * v);
+            S[j][2] = fmaf(decay, S[j][2], kd.z * v);
+            S[j][3] = fmaf(decay, S[j][3], kd.w * v);
+            o = fmaf(S[j][0], qd.x, o);
+            o = fmaf(S[j][1], qd.y, o);
+            o = fmaf(S[j][2], qd.z, o);
+            o = fmaf(S[j][3], qd.w, o);
+          }
+        }
+      } else {
+        const float g = bg[buf][tt], beta = bb[buf][tt];
+        float dot = 0.f;
+        float4 kd[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < RG) {
+            kd[j] = *(const float4 *)(tk + tt * Dp + 4 * (j * L + lane_in_col));
+            S[j][0] *= g; S[j][1] *= g; S[j][2] *= g; S[j][3] *= g;
+            dot = fmaf(S[j][0], kd[j].x, dot);
+            dot = fmaf(S[j][1], kd[j].y, dot);
+            dot = fmaf(S[j][2], kd[j].z, dot);
+            dot = fmaf(S[j][3], kd[j].w, dot);
+          }
+        }
+        for (int off = L >> 1; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        const float u = beta * (v - dot);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < RG) {
+            const float4 qd = *(const float4 *)(tq + tt * Dp + 4 * (j * L + lane_in_col));
+            S[j][0] = fmaf(kd[j].x, u, S[j][0]);
+            S[j][1] = fmaf(kd[j].y, u, S[j][1]);
+            S[j][2] = fmaf(kd[j].z, u, S[j][2]);
+            S[j][3] = fmaf(kd[j].w, u, S[j][3]);
+            o = fmaf(S[j][0], qd.x, o);
+            o = fmaf(S[j][1], qd.y, o);
+            o = fmaf(S[j][2], qd.z, o);
+            o = fmaf(S[j][3], qd.w, o);
+          }
+        }
+      }
+      for (int off = L >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (live && lane_in_col == 0) a.out[(size_t)(first_row + t0 + tt) * H * V + (size_t)h * V + c] = o;
+    }
+    if (next < n) store_small(nn, buf ^ 1);
+  }
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int d = 4 * (j * L + lane_in_col) + i;
+        if (j < RG && d < D) sp[d] = S[j][i];
+      }
+  }
+}
+
+extern "C" int g2b_state_scan_prompt(int mode, int dtype, const void *q, int q_stride, const void *k, int k_stride,
+                                     const void *v, int v_stride, int H, int G, int D, int V, const float *rope, int rot,
+                                     int interleaved, float q_scale, float k_scale, int unit_norm, float unit_eps,
+                                     const float *decay, const float *ab, const float *A_log, const float *dt_bias,
+                                     float *state, const int *seq_meta, int n_tokens, int n_seqs, float *qf, float *kf,
+                                     float *out, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_seqs <= 0) return 0;
+  if (D <= 0 || D > SCAN_MAX_D) G2B_REFUSE("state_scan: key size %d outside 1..%d", D, SCAN_MAX_D);
+  if (G <= 0 || H % G) G2B_REFUSE("state_scan: %d heads are not a multiple of %d query/key heads", H, G);
+  if (rope && (rot <= 0 || rot > D || (rot & 1))) G2B_REFUSE("state_scan: %d rotated entries of a head of %d", rot, D);
+  if (mode == 0 ? !decay : (!ab || !A_log || !dt_bias)) G2B_REFUSE("state_scan: mode %d lacks its decay inputs", mode);
+  if (!seq_meta) G2B_REFUSE("state_scan: the prompt kernel needs the step's table of sequences");
+  if (dtype != G2B_F32 && dtype != G2B_BF16) G2B_REFUSE("state_scan: unknown dtype %d", dtype);
+  const unsigned prep_blocks = (unsigned)(((long long)n_tokens * G + 3) / 4);
+  if (dtype == G2B_F32)
+    g2b_launch(scan_prep_kernel<float>, dim3(prep_blocks), dim3(128), 0, stream, (const float *)q, q_stride, (const float *)k,
+               k_stride, n_tokens, G, D, (const float2 *)rope, rot, interleaved, q_scale, k_scale, unit_norm, unit_eps, qf, kf);
+  else
+    g2b_launch(scan_prep_kernel<bf16>, dim3(prep_blocks), dim3(128), 0, stream, (const bf16 *)q, q_stride, (const bf16 *)k,
+               k_stride, n_tokens, G, D, (const float2 *)rope, rot, interleaved, q_scale, k_scale, unit_norm, unit_eps, qf, kf);
+  PScanArgs a;
+  a.qf = qf; a.kf = kf; a.v = v; a.v_stride = v_stride; a.H = H; a.G = G; a.D = D; a.V = V; a.decay = decay; a.ab = ab;
+  a.A_log = A_log; a.dt_bias = dt_bias; a.state = state; a.seq_meta = seq_meta; a.out = out;
+  a.L = 8;
+  while (a.L * 16 < D) a.L <<= 1;
+  a.Dp = (D + 4 * a.L - 1) / (4 * a.L) * (4 * a.L);
+  a.tile = a.Dp <= 128 ? 16 : (a.Dp <= 256 ? 8 : 4);            // q and k of a tile: 16 KB a buffer
+  const int cols = PSCAN_THREADS / a.L;
+  const size_t smem = (size_t)(4 * a.tile * a.Dp + 2 * a.tile * (cols + 2)) * sizeof(float);
+  const dim3 grid((V + cols - 1) / cols, H, n_seqs);
+  if (mode == 0) {
+    if (dtype == G2B_F32) g2b_launch(state_scan_prompt_kernel<float, 0>, grid, dim3(PSCAN_THREADS), smem, stream, a);
+    else g2b_launch(state_scan_prompt_kernel<bf16, 0>, grid, dim3(PSCAN_THREADS), smem, stream, a);
+  } else if (mode == 1) {
+    if (dtype == G2B_F32) g2b_launch(state_scan_prompt_kernel<float, 1>, grid, dim3(PSCAN_THREADS), smem, stream, a);
+    else g2b_launch(state_scan_prompt_kernel<bf16, 1>, grid, dim3(PSCAN_THREADS), smem, stream, a);
+  } else {
+    G2B_REFUSE("state_scan: unknown mode %d", mode);
+  }
+  return g2b_check_launch("state_scan_prompt");
+}
+
+// ---------------------------------------------------------------------------
 // per-head norm of the scan's output, times a gate
 // ---------------------------------------------------------------------------
 template <typename T>

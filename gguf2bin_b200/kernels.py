@@ -643,14 +643,25 @@ def state_scan(q, k, v, state, ctx, out32, heads, qk_heads, qk_dim, v_dim, *, de
             _need(t, torch.float32, "decay inputs")
     if k.dtype != q.dtype or v.dtype != q.dtype:
         raise KernelError("state_scan: q, k and v must have one dtype")
+    common = [mode, _code(q.dtype), _ptr(q), _dense_rows(q, "q"), _ptr(k), _dense_rows(k, "k"), _ptr(v),
+              _dense_rows(v, "v"), heads, qk_heads, qk_dim, v_dim, _ptr(rope), rotary_dim, 1 if interleaved else 0,
+              q_scale, k_scale, 0 if unit_eps is None else 1, unit_eps or 0.0, _ptr(decay), _ptr(ab), _ptr(a_log),
+              _ptr(dt_bias), _ptr(state)]
+    types = [c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+             c_int, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+    if ctx.seq_meta is not None and T > ctx.n_seqs:
+        # a prompt step: q and k are prepared once (rotation or unit norm, scales; float), then a scan
+        # that fetches the next tokens while it works on the ones it has
+        qf = ctx.workspace.buffer("scan.q", (T, qk_heads * qk_dim), torch.float32)
+        kf = ctx.workspace.buffer("scan.k", (T, qk_heads * qk_dim), torch.float32)
+        f = _fn("seq_mix.cu", "g2b_state_scan_prompt",
+                types + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+        _call(f, *common, _ptr(ctx.seq_meta), T, ctx.n_seqs, _ptr(qf), _ptr(kf), _ptr(out32), _stream())
+        count_launches(1)
+        return
     f = _fn("seq_mix.cu", "g2b_state_scan",
-            [c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
-             c_int, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
-    _call(f, mode, _code(q.dtype), _ptr(q), _dense_rows(q, "q"), _ptr(k), _dense_rows(k, "k"), _ptr(v),
-          _dense_rows(v, "v"), heads, qk_heads, qk_dim, v_dim, _ptr(rope), rotary_dim, 1 if interleaved else 0,
-          q_scale, k_scale, 0 if unit_eps is None else 1, unit_eps or 0.0, _ptr(decay), _ptr(ab), _ptr(a_log),
-          _ptr(dt_bias), _ptr(state), _ptr(ctx.tok_pos), _ptr(ctx.seq_slots), _ptr(ctx.seq_meta), T, ctx.n_seqs,
+            types + [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _call(f, *common, _ptr(ctx.tok_pos), _ptr(ctx.seq_slots), _ptr(ctx.seq_meta), T, ctx.n_seqs,
           _ptr(out32), _stream())
 
 
