@@ -335,7 +335,107 @@ moe_gemm_mma_kernel(const bf16 *__restrict__ A, int a_stride, const int *__restr
       }
 }
 
+// ---------------------------------------------------------------------------
+// the same for a step of few rows (decoding): a warp takes four output columns of one row and
+// streams their weight rows with 16-byte loads, the row's K entries dealt to the lanes
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float dot_chunk(const uint4 &w, const uint4 &x, float acc, bf16) {
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w}, xx[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc = fmaf(__uint_as_float(ww[i] << 16), __uint_as_float(xx[i] << 16), acc);
+    acc = fmaf(__uint_as_float(ww[i] & 0xffff0000u), __uint_as_float(xx[i] & 0xffff0000u), acc);
+  }
+  return acc;
+}
+__device__ __forceinline__ float dot_chunk(const uint4 &w, const uint4 &x, float acc, float) {
+  acc = fmaf(__uint_as_float(w.x), __uint_as_float(x.x), acc);
+  acc = fmaf(__uint_as_float(w.y), __uint_as_float(x.y), acc);
+  acc = fmaf(__uint_as_float(w.z), __uint_as_float(x.z), acc);
+  return fmaf(__uint_as_float(w.w), __uint_as_float(x.w), acc);
+}
+
+#define MV_COLS 4            // columns a warp computes at a time
+template <typename T, bool SWIGLU>
+__global__ void __launch_bounds__(128)
+moe_gemv_kernel(const T *__restrict__ A, int a_stride, const int *__restrict__ row_pair, int pairs_per_token, int gather,
+                const int *__restrict__ idx, const T *__restrict__ W, int N, int K, const int *__restrict__ plan,
+                int n_real, void *__restrict__ out, int out_f32) {
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.y;
+  if (r >= plan[1 + n_real]) return;                     // rows in use
+  const int pair = row_pair[r];
+  const int e = idx[pair];
+  constexpr int EPL = 16 / sizeof(T);                    // entries per 16-byte load
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * 4 + warp) * MV_COLS;
+  if (n0 >= N) return;
+  const T *a = A + (size_t)(gather ? pair / pairs_per_token : r) * a_stride;
+  const T *We = W + (size_t)e * (SWIGLU ? 2 : 1) * N * K;
+  const int chunks = K / EPL;
+  float acc[SWIGLU ? 2 : 1][MV_COLS];
+#pragma unroll
+  for (int s = 0; s < (SWIGLU ? 2 : 1); ++s)
+#pragma unroll
+    for (int j = 0; j < MV_COLS; ++j) acc[s][j] = 0.f;
+#pragma unroll 2
+  for (int c = lane; c < chunks; c += 32) {
+    const uint4 x = *(const uint4 *)(a + (size_t)c * EPL);
+    uint4 w[SWIGLU ? 2 : 1][MV_COLS];
+#pragma unroll
+    for (int s = 0; s < (SWIGLU ? 2 : 1); ++s)
+#pragma unroll
+      for (int j = 0; j < MV_COLS; ++j) {
+        const int n = min(n0 + j, N - 1);
+        w[s][j] = *(const uint4 *)(We + ((size_t)s * N + n) * K + (size_t)c * EPL);
+      }
+#pragma unroll
+    for (int s = 0; s < (SWIGLU ? 2 : 1); ++s)
+#pragma unroll
+      for (int j = 0; j < MV_COLS; ++j) acc[s][j] = dot_chunk(w[s][j], x, acc[s][j], T());
+  }
+#pragma unroll
+  for (int j = 0; j < MV_COLS; ++j) {
+    float v = warp_sum(acc[0][j]);
+    if (SWIGLU) v = silu_f(v) * warp_sum(acc[SWIGLU ? 1 : 0][j]);
+    if (lane == 0 && n0 + j < N) {
+      const size_t at = (size_t)r * N + n0 + j;
+      if (out_f32) ((float *)out)[at] = v;
+      else ((T *)out)[at] = from_f32<T>(v);
+    }
+  }
+}
+
 extern "C" int g2b_moe_tile_rows() { return MG_BM; }
+
+template <typename T>
+static void launch_gemv(const void *A, int a_stride, const int *row_pair, int pairs_per_token, int gather, const int *idx,
+                        const void *W, int N, int K, const int *plan, int n_real, int n_rows, int swiglu, void *out,
+                        int out_f32, cudaStream_t stream) {
+  const dim3 grid((N + 4 * MV_COLS - 1) / (4 * MV_COLS), n_rows);
+  if (swiglu)
+    g2b_launch(moe_gemv_kernel<T, true>, grid, dim3(128), 0, stream, (const T *)A, a_stride, row_pair, pairs_per_token,
+               gather, idx, (const T *)W, N, K, plan, n_real, out, out_f32);
+  else
+    g2b_launch(moe_gemv_kernel<T, false>, grid, dim3(128), 0, stream, (const T *)A, a_stride, row_pair, pairs_per_token,
+               gather, idx, (const T *)W, N, K, plan, n_real, out, out_f32);
+}
+
+// Few rows: `row_pair` (row -> pair) and `idx` (pair -> expert) are both needed; `gather` says whether
+// row r reads A[pair / pairs_per_token] or A[r].
+extern "C" int g2b_moe_gemv(const void *A, int dtype, int a_stride, const int *row_pair, int pairs_per_token, int gather,
+                            const int *idx, const void *W, int N, int K, const int *plan, int n_real, int n_rows,
+                            int swiglu, void *out, int out_f32, cudaStream_t stream) {
+  if (n_rows <= 0 || N <= 0) return 0;
+  const int epl = dtype == G2B_BF16 ? 8 : 4;
+  if (K % epl || a_stride % epl || (((uintptr_t)A | (uintptr_t)W) & 15))
+    G2B_REFUSE("moe_gemv: K = %d or the rows' distance %d is no multiple of %d, or a pointer is off 16 bytes", K, a_stride, epl);
+  if (dtype == G2B_F32) launch_gemv<float>(A, a_stride, row_pair, pairs_per_token, gather, idx, W, N, K, plan, n_real, n_rows, swiglu, out, out_f32, stream);
+  else if (dtype == G2B_BF16) launch_gemv<bf16>(A, a_stride, row_pair, pairs_per_token, gather, idx, W, N, K, plan, n_real, n_rows, swiglu, out, out_f32, stream);
+  else G2B_REFUSE("moe_gemv: unknown dtype %d", dtype);
+  return g2b_check_launch("moe_gemv");
+}
 
 extern "C" int g2b_moe_gemm(const void *A, int dtype, int a_stride, const int *row_pair, int pairs_per_token,
                             const void *W, int N, int K, const int *plan, int n_real, int max_tiles, int swiglu,

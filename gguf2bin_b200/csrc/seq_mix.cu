@@ -505,20 +505,17 @@ struct PScanArgs {
   int L, Dp, tile;
 };
 
-template <typename T, int MODE>
+template <typename T, int MODE, int L>
 __global__ void __launch_bounds__(PSCAN_THREADS)
 state_scan_prompt_kernel(const PScanArgs a) {
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(16) float psm[];
-  const int D = a.D, V = a.V, H = a.H, L = a.L, Dp = a.Dp, TT = a.tile;
-  const int cols = PSCAN_THREADS / L;
-  float *bq[2], *bk[2], *bv[2], *bg[2], *bb[2];
-  {
-    float *p = psm;
-    for (int i = 0; i < 2; ++i) { bq[i] = p; p += TT * Dp; bk[i] = p; p += TT * Dp; }
-    for (int i = 0; i < 2; ++i) { bv[i] = p; p += TT * cols; bg[i] = p; p += TT; bb[i] = p; p += TT; }
-  }
+  constexpr int cols = PSCAN_THREADS / L;
+  const int D = a.D, V = a.V, H = a.H, Dp = a.Dp, TT = a.tile;
+  // two buffers, each: q [TT, Dp], k [TT, Dp]; behind them two of v [TT, cols], gate [TT], strength [TT]
+  const int qk_buf = 2 * TT * Dp, small_buf = TT * (cols + 2);
+  float *small = psm + 2 * qk_buf;
   const int b = blockIdx.z, h = blockIdx.y;
   const int qk_head = h / (H / a.G);
   const int lane_in_col = threadIdx.x % L, col_local = threadIdx.x / L;
@@ -540,39 +537,41 @@ state_scan_prompt_kernel(const PScanArgs a) {
   if (MODE == 0) decay = a.decay[h];
   else { A = expf(a.A_log[h]); dt = a.dt_bias[h]; }
   const T *vg = (const T *)a.v;
-  // rows from D on stay zero in both buffers
-  for (int i = threadIdx.x; i < 4 * TT * Dp; i += PSCAN_THREADS) psm[i] = 0.f;
+  for (int i = threadIdx.x; i < 2 * qk_buf; i += PSCAN_THREADS) psm[i] = 0.f;     // rows from D on stay zero
   __syncthreads();
 
   auto fetch_qk = [&](int t0, int nt, int buf) {
     const float *qsrc = a.qf + ((size_t)(first_row + t0) * a.G + qk_head) * D;
     const float *ksrc = a.kf + ((size_t)(first_row + t0) * a.G + qk_head) * D;
     const size_t row = (size_t)a.G * D;
+    float *dq = psm + buf * qk_buf, *dk = dq + TT * Dp;
     if (vec) {
       const int per = D >> 2;
       for (int i = threadIdx.x; i < nt * per; i += PSCAN_THREADS) {
         const int tt = i / per, p = i % per;
-        cp_async_f4(bq[buf] + tt * Dp + 4 * p, qsrc + tt * row + 4 * p);
-        cp_async_f4(bk[buf] + tt * Dp + 4 * p, ksrc + tt * row + 4 * p);
+        cp_async_f4(dq + tt * Dp + 4 * p, qsrc + tt * row + 4 * p);
+        cp_async_f4(dk + tt * Dp + 4 * p, ksrc + tt * row + 4 * p);
       }
     } else {
       for (int i = threadIdx.x; i < nt * D; i += PSCAN_THREADS) {
         const int tt = i / D, p = i % D;
-        bq[buf][tt * Dp + p] = qsrc[tt * row + p];
-        bk[buf][tt * Dp + p] = ksrc[tt * row + p];
+        dq[tt * Dp + p] = qsrc[tt * row + p];
+        dk[tt * Dp + p] = ksrc[tt * row + p];
       }
     }
     cp_async_commit_group();
   };
   // the small per-token values go through registers: loaded before the tile in work is computed,
   // stored behind it
-  float rv[4] = {0.f, 0.f, 0.f, 0.f}, rg = 0.f, rb = 0.f;          // TT * cols <= 4 * 128
+  float rv0 = 0.f, rv1 = 0.f, rg = 0.f, rb = 0.f;                   // TT * cols <= 256 = 2 * threads
   auto load_small = [&](int t0, int nt) {
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int i = threadIdx.x + u * PSCAN_THREADS;
-      const int tt = i / cols, cc = i % cols, col = blockIdx.x * cols + cc;
-      rv[u] = (tt < nt && col < V) ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * V + col]) : 0.f;
+    {
+      const int i = threadIdx.x, tt = i / cols, col = blockIdx.x * cols + i % cols;
+      rv0 = (tt < nt && col < V) ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * V + col]) : 0.f;
+    }
+    {
+      const int i = threadIdx.x + PSCAN_THREADS, tt = i / cols, col = blockIdx.x * cols + i % cols;
+      rv1 = (tt < nt && col < V) ? to_f32(vg[(size_t)(first_row + t0 + tt) * a.v_stride + (size_t)h * V + col]) : 0.f;
     }
     if (MODE == 1 && threadIdx.x < nt) {
       const size_t row = (size_t)(first_row + t0 + threadIdx.x) * 2 * H;
@@ -581,14 +580,12 @@ state_scan_prompt_kernel(const PScanArgs a) {
     }
   };
   auto store_small = [&](int nt, int buf) {
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int i = threadIdx.x + u * PSCAN_THREADS;
-      if (i < TT * cols) bv[buf][i] = rv[u];
-    }
+    float *dv = small + buf * small_buf;
+    if (threadIdx.x < TT * cols) dv[threadIdx.x] = rv0;
+    if (threadIdx.x + PSCAN_THREADS < TT * cols) dv[threadIdx.x + PSCAN_THREADS] = rv1;
     if (MODE == 1 && threadIdx.x < nt) {
-      bg[buf][threadIdx.x] = expf(-A * softplus_f(rg + dt));
-      bb[buf][threadIdx.x] = sigmoid_f(rb);
+      dv[TT * cols + threadIdx.x] = expf(-A * softplus_f(rg + dt));
+      dv[TT * cols + TT + threadIdx.x] = sigmoid_f(rb);
     }
   };
 
@@ -596,6 +593,7 @@ state_scan_prompt_kernel(const PScanArgs a) {
   load_small(0, min(TT, n));
   store_small(min(TT, n), 0);
   int buf = 0;
+  const size_t out_row = (size_t)H * V;
   for (int t0 = 0; t0 < n; t0 += TT, buf ^= 1) {
     const int nt = min(TT, n - t0);
     const int next = t0 + TT, nn = min(TT, n - next);
@@ -605,60 +603,60 @@ state_scan_prompt_kernel(const PScanArgs a) {
       fetch_qk(next, nn, buf ^ 1);
       load_small(next, nn);
     }
-    const float *tq = bq[buf], *tk = bk[buf];
-    for (int tt = 0; tt < nt; ++tt) {
-      const float v = bv[buf][tt * cols + col_local];
-      float o = 0.f;
+    const float *qp = psm + buf * qk_buf + 4 * lane_in_col;
+    const float *kp = qp + TT * Dp;
+    const float *vp = small + buf * small_buf + col_local;
+    const float *gp = small + buf * small_buf + TT * cols, *bp = gp + TT;
+    float *op = a.out + (size_t)(first_row + t0) * out_row + (size_t)h * V + c;
+#pragma unroll 4
+    for (int tt = 0; tt < nt; ++tt, qp += Dp, kp += Dp, vp += cols, op += out_row) {
+      const float v = *vp;
+      float o[4] = {0.f, 0.f, 0.f, 0.f};
       if (MODE == 0) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (j < RG) {
-            const float4 kd = *(const float4 *)(tk + tt * Dp + 4 * (j * L + lane_in_col));
-            const float4 qd = *(const float4 *)(tq + tt * Dp + 4 * (j * L + lane_in_col));
+            const float4 kd = *(const float4 *)(kp + 4 * j * L);
+            const float4 qd = *(const float4 *)(qp + 4 * j * L);
             S[j][0] = fmaf(decay, S[j][0], kd.x * v);
             S[j][1] = fmaf(decay, S[j][1], kd.y * v);
             S[j][2] = fmaf(decay, S[j][2], kd.z * v);
             S[j][3] = fmaf(decay, S[j][3], kd.w * v);
-            o = fmaf(S[j][0], qd.x, o);
-            o = fmaf(S[j][1], qd.y, o);
-            o = fmaf(S[j][2], qd.z, o);
-            o = fmaf(S[j][3], qd.w, o);
+            o[j] = fmaf(S[j][3], qd.w, fmaf(S[j][2], qd.z, fmaf(S[j][1], qd.y, S[j][0] * qd.x)));
           }
         }
       } else {
-        const float g = bg[buf][tt], beta = bb[buf][tt];
-        float dot = 0.f;
+        const float g = gp[tt], beta = bp[tt];
+        float dot[4] = {0.f, 0.f, 0.f, 0.f};
         float4 kd[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (j < RG) {
-            kd[j] = *(const float4 *)(tk + tt * Dp + 4 * (j * L + lane_in_col));
+            kd[j] = *(const float4 *)(kp + 4 * j * L);
             S[j][0] *= g; S[j][1] *= g; S[j][2] *= g; S[j][3] *= g;
-            dot = fmaf(S[j][0], kd[j].x, dot);
-            dot = fmaf(S[j][1], kd[j].y, dot);
-            dot = fmaf(S[j][2], kd[j].z, dot);
-            dot = fmaf(S[j][3], kd[j].w, dot);
+            dot[j] = fmaf(S[j][3], kd[j].w, fmaf(S[j][2], kd[j].z, fmaf(S[j][1], kd[j].y, S[j][0] * kd[j].x)));
           }
         }
-        for (int off = L >> 1; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-        const float u = beta * (v - dot);
+        float dsum = (dot[0] + dot[1]) + (dot[2] + dot[3]);
+#pragma unroll
+        for (int off = L >> 1; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+        const float u = beta * (v - dsum);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (j < RG) {
-            const float4 qd = *(const float4 *)(tq + tt * Dp + 4 * (j * L + lane_in_col));
+            const float4 qd = *(const float4 *)(qp + 4 * j * L);
             S[j][0] = fmaf(kd[j].x, u, S[j][0]);
             S[j][1] = fmaf(kd[j].y, u, S[j][1]);
             S[j][2] = fmaf(kd[j].z, u, S[j][2]);
             S[j][3] = fmaf(kd[j].w, u, S[j][3]);
-            o = fmaf(S[j][0], qd.x, o);
-            o = fmaf(S[j][1], qd.y, o);
-            o = fmaf(S[j][2], qd.z, o);
-            o = fmaf(S[j][3], qd.w, o);
+            o[j] = fmaf(S[j][3], qd.w, fmaf(S[j][2], qd.z, fmaf(S[j][1], qd.y, S[j][0] * qd.x)));
           }
         }
       }
-      for (int off = L >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-      if (live && lane_in_col == 0) a.out[(size_t)(first_row + t0 + tt) * H * V + (size_t)h * V + c] = o;
+      float osum = (o[0] + o[1]) + (o[2] + o[3]);
+#pragma unroll
+      for (int off = L >> 1; off > 0; off >>= 1) osum += __shfl_xor_sync(0xffffffffu, osum, off);
+      if (live && lane_in_col == 0) *op = osum;
     }
     if (next < n) store_small(nn, buf ^ 1);
   }
@@ -671,6 +669,13 @@ state_scan_prompt_kernel(const PScanArgs a) {
         if (j < RG && d < D) sp[d] = S[j][i];
       }
   }
+}
+
+template <typename T, int MODE>
+static void launch_scan_prompt(const PScanArgs &a, dim3 grid, size_t smem, cudaStream_t stream) {
+  if (a.L == 8) g2b_launch(state_scan_prompt_kernel<T, MODE, 8>, grid, dim3(PSCAN_THREADS), smem, stream, a);
+  else if (a.L == 16) g2b_launch(state_scan_prompt_kernel<T, MODE, 16>, grid, dim3(PSCAN_THREADS), smem, stream, a);
+  else g2b_launch(state_scan_prompt_kernel<T, MODE, 32>, grid, dim3(PSCAN_THREADS), smem, stream, a);
 }
 
 extern "C" int g2b_state_scan_prompt(int mode, int dtype, const void *q, int q_stride, const void *k, int k_stride,
@@ -696,19 +701,25 @@ extern "C" int g2b_state_scan_prompt(int mode, int dtype, const void *q, int q_s
   PScanArgs a;
   a.qf = qf; a.kf = kf; a.v = v; a.v_stride = v_stride; a.H = H; a.G = G; a.D = D; a.V = V; a.decay = decay; a.ab = ab;
   a.A_log = A_log; a.dt_bias = dt_bias; a.state = state; a.seq_meta = seq_meta; a.out = out;
+  // Lanes per column: at least D / 16; more while the step has few columns, so that every scheduler
+  // of the GPU gets a few warps (a token's work in a warp is a chain of short dependent steps).
   a.L = 8;
   while (a.L * 16 < D) a.L <<= 1;
+  {
+    const long long columns = (long long)n_seqs * H * V;
+    while (a.L < 32 && columns * a.L * 2 <= 32LL * 2400) a.L <<= 1;
+  }
   a.Dp = (D + 4 * a.L - 1) / (4 * a.L) * (4 * a.L);
   a.tile = a.Dp <= 128 ? 16 : (a.Dp <= 256 ? 8 : 4);            // q and k of a tile: 16 KB a buffer
   const int cols = PSCAN_THREADS / a.L;
   const size_t smem = (size_t)(4 * a.tile * a.Dp + 2 * a.tile * (cols + 2)) * sizeof(float);
   const dim3 grid((V + cols - 1) / cols, H, n_seqs);
   if (mode == 0) {
-    if (dtype == G2B_F32) g2b_launch(state_scan_prompt_kernel<float, 0>, grid, dim3(PSCAN_THREADS), smem, stream, a);
-    else g2b_launch(state_scan_prompt_kernel<bf16, 0>, grid, dim3(PSCAN_THREADS), smem, stream, a);
+    if (dtype == G2B_F32) launch_scan_prompt<float, 0>(a, grid, smem, stream);
+    else launch_scan_prompt<bf16, 0>(a, grid, smem, stream);
   } else if (mode == 1) {
-    if (dtype == G2B_F32) g2b_launch(state_scan_prompt_kernel<float, 1>, grid, dim3(PSCAN_THREADS), smem, stream, a);
-    else g2b_launch(state_scan_prompt_kernel<bf16, 1>, grid, dim3(PSCAN_THREADS), smem, stream, a);
+    if (dtype == G2B_F32) launch_scan_prompt<float, 1>(a, grid, smem, stream);
+    else launch_scan_prompt<bf16, 1>(a, grid, smem, stream);
   } else {
     G2B_REFUSE("state_scan: unknown mode %d", mode);
   }

@@ -20,7 +20,7 @@ __all__ = ["KernelError", "KernelBuildError", "embed_rows", "rmsnorm", "qknorm_r
            "attention", "sample_rows", "sample_filtered", "recent_set", "seed_slots", "embed_pair_norm",
            "canon_conv", "norm_canon_single", "latent_keep", "head_product", "head_gate", "gated_add", "xielu",
            "proj_norm_rope_cache", "rotate_heads", "short_conv", "state_scan", "head_norm_gate", "gate_mul",
-           "norm_add", "moe_route", "moe_plan", "moe_gemm", "moe_combine", "moe_tile_rows"]
+           "norm_add", "moe_route", "moe_plan", "moe_gemm", "moe_gemv", "moe_combine", "moe_tile_rows"]
 
 F32, BF16 = 0, 1
 EPI_STORE_F32, EPI_STORE_BF16, EPI_ACCUM_F32 = 0, 1, 2
@@ -742,6 +742,25 @@ def moe_gemm(a, row_pair, pairs_per_token: int, w, n_out: int, plan, n_real: int
     _call(f, _ptr(a), _code(a.dtype), _dense_rows(a, "a"), _ptr(row_pair), pairs_per_token, _ptr(w), n_out,
           a.shape[1], _ptr(plan), n_real, max_tiles, 1 if swiglu else 0, _ptr(out),
           1 if out.dtype == torch.float32 else 0, _stream())
+
+
+def moe_gemv(a, row_pair, pairs_per_token: int, gather: bool, idx, w, n_out: int, plan, n_real: int, n_rows: int,
+             swiglu: bool, out) -> bool:
+    """``moe_gemm`` for a step of few rows: a warp per four output columns of one row, the weight rows
+    streamed with 16-byte loads.  ``gather``: row r reads a[pair / pairs_per_token], else a[r].  False
+    when the sizes do not allow 16-byte loads (the caller then takes ``moe_gemm``)."""
+    if w.dtype != a.dtype:
+        raise KernelError("moe_gemv: activations and expert matrices must have one dtype")
+    per = 8 if a.dtype == torch.bfloat16 else 4
+    if a.shape[1] % per or a.stride(0) % per or a.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    f = _fn("moe.cu", "g2b_moe_gemv",
+            [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+             c_int, c_void_p, c_int, c_void_p])
+    _call(f, _ptr(a), _code(a.dtype), _dense_rows(a, "a"), _ptr(row_pair), pairs_per_token, 1 if gather else 0,
+          _ptr(idx), _ptr(w), n_out, a.shape[1], _ptr(plan), n_real, n_rows, 1 if swiglu else 0, _ptr(out),
+          1 if out.dtype == torch.float32 else 0, _stream())
+    return True
 
 
 def moe_combine(rows32, pair_row, weight, x_self32, top: int, out32) -> None:

@@ -160,6 +160,7 @@ class RoutedExperts:
     grouped product for gate and up with the activation in its epilogue and one for down; nothing
     comes back to the host, so the step may be replayed from a CUDA graph."""
     graph_safe = True
+    FEW_ROWS = 128            # (token, choice) pairs up to which every row streams its expert's matrices by itself
 
     def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
         self.E, self.I = int(spec["n_experts"]), int(spec.get("n_identity") or 0)
@@ -235,8 +236,14 @@ class RoutedExperts:
             wt = self.w_gate_up.dtype                     # matrices stored in 32-bit keep their products there
             mid = ws.buffer("moe.mid", (n_pairs, self.inter), wt)
             a = h if h.dtype == wt else h.to(wt)
-            kernels.moe_gemm(a, row_pair, top, self.w_gate_up, self.inter, plan, E, max_tiles, True, mid)
-            kernels.moe_gemm(mid, None, 1, self.w_down, self.hidden, plan, E, max_tiles, False, rows32)
+            # few rows (decoding): every row streams its expert's matrices; else tiles of rows per expert
+            few = n_pairs <= self.FEW_ROWS
+            if not (few and kernels.moe_gemv(a, row_pair, top, True, idx, self.w_gate_up, self.inter, plan, E,
+                                             n_pairs, True, mid)):
+                kernels.moe_gemm(a, row_pair, top, self.w_gate_up, self.inter, plan, E, max_tiles, True, mid)
+            if not (few and kernels.moe_gemv(mid, row_pair, top, False, idx, self.w_down, self.hidden, plan, E,
+                                             n_pairs, False, rows32)):
+                kernels.moe_gemm(mid, None, 1, self.w_down, self.hidden, plan, E, max_tiles, False, rows32)
         if x_self32 is None:
             x_self32 = h if h.dtype == torch.float32 else h.float()
         kernels.moe_combine(rows32, pair_row, weight, x_self32, top, out32)

@@ -270,10 +270,13 @@ def test_routed_experts_part(E, I, top, ff, width, dtype):
         part.forward_into(dev(h[:n], DTYPES[dtype]), ctx, y, dev(h[:n]))
         outs[n] = y.cpu().numpy()
         close(outs[n], ref[:n], dtype, f"routed experts, {n} rows")
-    if dtype == "float32":        # one product kernel whatever the number of rows: the same bits
-        assert np.array_equal(outs[77][:5], outs[5]) and np.array_equal(outs[5][:1], outs[1])
-    else:                         # the router's product is a kernel chosen by the step's rows; nothing else differs
-        assert np.abs(outs[77][:5] - outs[5]).max() < 1e-5 and np.abs(outs[5][:1] - outs[1]).max() < 1e-5
+    # a step of few rows and one of many take different product kernels (rounding apart); within one
+    # kind a row's bits do not depend on the rows beside it
+    assert np.abs(outs[77][:5] - outs[5]).max() < 1e-5 * max(1.0, np.abs(ref).max())
+    if dtype == "float32":
+        assert np.array_equal(outs[5][:1], outs[1])
+    else:                         # the router's product is a kernel chosen by the step's rows too
+        assert np.abs(outs[5][:1] - outs[1]).max() < 1e-5 * max(1.0, np.abs(ref).max())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
