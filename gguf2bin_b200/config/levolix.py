@@ -99,7 +99,8 @@ def _feed_forward(mlp, where: str):
                           f"is not a feed-forward of {ARCHITECTURE} (known: 'moe', or null for none)")
     r = _get(mlp, "router")
     return PartSpec.make(
-        "routed_experts", n_experts=_int(r, "experts", minimum=0), n_identity=_int(r, "identity", minimum=0),
+        "routed_experts", n_experts=_int(r, "experts", minimum=0),
+        n_identity=_int(r, "identity", minimum=0) if "identity" in r else 0,
         top=_int(r, "top"), intermediate_size=_int(mlp, "expert.ff"), correction=True, renormalise=False,
         names=(("router", "mlp.router"), ("correction", "mlp.correction"), ("gate", "mlp.e{}.gate"),
                ("up", "mlp.e{}.up"), ("down", "mlp.e{}.down")))

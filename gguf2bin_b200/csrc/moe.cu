@@ -336,6 +336,122 @@ moe_gemm_mma_kernel(const bf16 *__restrict__ A, int a_stride, const int *__restr
 }
 
 // ---------------------------------------------------------------------------
+// many rows per expert: tiles of 128 rows x 64 columns, eight warps (4 x 2, each 32 x 32), operands
+// fetched one k-step ahead with cp.async, fragments read with ldmatrix
+// ---------------------------------------------------------------------------
+#define MW_BM 128
+#define MW_BK 32
+#define MW_LD (MW_BK + 8)
+template <bool SWIGLU>
+__global__ void __launch_bounds__(256)
+moe_gemm_wide_kernel(const bf16 *__restrict__ A, int a_stride, const int *__restrict__ row_pair, int pairs_per_token,
+                     const bf16 *__restrict__ W, int N, int K, const int *__restrict__ plan, int n_real,
+                     void *__restrict__ out, int out_f32) {
+  pdl_launch();
+  pdl_wait();
+  constexpr int S = SWIGLU ? 2 : 1;
+  __shared__ __align__(16) bf16 As[2][MW_BM][MW_LD];
+  __shared__ __align__(16) bf16 Bs[2][S][MG_BN][MW_LD];
+  __shared__ int src_row[MW_BM];
+  // the plan's tiles are MG_BM rows; this kernel takes MW_BM / MG_BM of them at a time when they follow
+  // one another in ONE expert's range: blockIdx.y counts groups of plan tiles, and a group that starts
+  // inside an expert's range but is not its first of this size is skipped
+  const int per = MW_BM / MG_BM;
+  const int tile = blockIdx.y;
+  const int n_tiles = plan[0];
+  if (tile >= n_tiles) return;
+  const int *tl = plan + PLAN_TILES_AT(n_real) + 3 * tile;
+  const int e = tl[0], row0 = tl[1];
+  const int first = plan[1 + e], end = plan[2 + e];        // the expert's rows
+  if ((row0 - first) % MW_BM) return;                      // not the first plan tile of a wide tile
+  const int rows = min(MW_BM, end - row0);
+  (void)per;
+  const int n0 = blockIdx.x * MG_BN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp >> 1, wn = warp & 1;
+  if (tid < MW_BM) {
+    int r = -1;
+    if (tid < rows) r = row_pair ? row_pair[row0 + tid] / pairs_per_token : row0 + tid;
+    src_row[tid] = r;
+  }
+  __syncthreads();
+  const bf16 *We = W + (size_t)e * (size_t)S * N * K;
+  float acc[S][2][4][4];
+#pragma unroll
+  for (int s = 0; s < S; ++s)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int f = 0; f < 4; ++f) acc[s][i][j][f] = 0.f;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  auto load_stage = [&](int st, int k0) {
+    for (int i = tid; i < MW_BM * (MW_BK / 8); i += 256) {
+      const int r = i >> 2, p = i & 3;
+      const int sr = src_row[r];
+      bf16 *dst = &As[st][r][p * 8];
+      if (sr >= 0 && k0 + p * 8 < K) cp_async_16(smem_u32(dst), A + (size_t)sr * a_stride + k0 + p * 8);
+      else *(uint4 *)dst = zero;
+    }
+    for (int i = tid; i < S * MG_BN * (MW_BK / 8); i += 256) {
+      const int s = i / (MG_BN * 4), c = (i >> 2) % MG_BN, p = i & 3;
+      bf16 *dst = &Bs[st][s][c][p * 8];
+      if (n0 + c < N && k0 + p * 8 < K) cp_async_16(smem_u32(dst), We + ((size_t)s * N + n0 + c) * K + k0 + p * 8);
+      else *(uint4 *)dst = zero;
+    }
+    cp_async_commit();
+  };
+  const int KT = (K + MW_BK - 1) / MW_BK;
+  load_stage(0, 0);
+  for (int kt = 0; kt < KT; ++kt) {
+    const int st = kt & 1;
+    if (kt + 1 < KT) {
+      load_stage(st ^ 1, (kt + 1) * MW_BK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MW_BK; kk += 16) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        ldmatrix_x4(a[i], smem_u32(&As[st][wm * 32 + 16 * i + (lane & 15)][kk + (lane >> 4) * 8]));
+#pragma unroll
+      for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int j2 = 0; j2 < 2; ++j2) {
+          uint32_t b[4];
+          ldmatrix_x4(b, smem_u32(&Bs[st][s][wn * 32 + 16 * j2 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]));
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            mma_bf16_16816(acc[s][i][2 * j2], a[i], b[0], b[1]);
+            mma_bf16_16816(acc[s][i][2 * j2 + 1], a[i], b[2], b[3]);
+          }
+        }
+    }
+    __syncthreads();
+  }
+  const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        const int r = wm * 32 + 16 * i + g + (f >> 1) * 8;
+        const int c = n0 + wn * 32 + 8 * j + 2 * q + (f & 1);
+        if (r >= rows || c >= N) continue;
+        const float v = SWIGLU ? silu_f(acc[0][i][j][f]) * acc[S - 1][i][j][f] : acc[0][i][j][f];
+        const size_t at = (size_t)(row0 + r) * N + c;
+        if (out_f32) ((float *)out)[at] = v;
+        else ((bf16 *)out)[at] = __float2bfloat16_rn(v);
+      }
+}
+
+// ---------------------------------------------------------------------------
 // the same for a step of few rows (decoding): a warp takes four output columns of one row and
 // streams their weight rows with 16-byte loads, the row's K entries dealt to the lanes
 // ---------------------------------------------------------------------------
@@ -451,7 +567,15 @@ extern "C" int g2b_moe_gemm(const void *A, int dtype, int a_stride, const int *r
                  pairs_per_token, (const float *)W, N, K, plan, n_real, out, out_f32);
   } else if (dtype == G2B_BF16) {
     const bool mma = K % 8 == 0 && a_stride % 8 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0;
-    if (mma && swiglu)
+    // many rows an expert (a prompt step): the wide tiles
+    const bool wide = mma && max_tiles > 3 * n_real + 8;
+    if (wide && swiglu)
+      g2b_launch(moe_gemm_wide_kernel<true>, grid, dim3(256), 0, stream, (const bf16 *)A, a_stride, row_pair,
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+    else if (wide)
+      g2b_launch(moe_gemm_wide_kernel<false>, grid, dim3(256), 0, stream, (const bf16 *)A, a_stride, row_pair,
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+    else if (mma && swiglu)
       g2b_launch(moe_gemm_mma_kernel<true>, grid, dim3(128), 0, stream, (const bf16 *)A, a_stride, row_pair,
                  pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
     else if (mma)

@@ -516,6 +516,7 @@ state_scan_prompt_kernel(const PScanArgs a) {
   // two buffers, each: q [TT, Dp], k [TT, Dp]; behind them two of v [TT, cols], gate [TT], strength [TT]
   const int qk_buf = 2 * TT * Dp, small_buf = TT * (cols + 2);
   float *small = psm + 2 * qk_buf;
+  float *po = small + 2 * small_buf;               // [TT, threads]: every lane's share of a token's read-out
   const int b = blockIdx.z, h = blockIdx.y;
   const int qk_head = h / (H / a.G);
   const int lane_in_col = threadIdx.x % L, col_local = threadIdx.x / L;
@@ -545,13 +546,13 @@ state_scan_prompt_kernel(const PScanArgs a) {
     const float *ksrc = a.kf + ((size_t)(first_row + t0) * a.G + qk_head) * D;
     const size_t row = (size_t)a.G * D;
     float *dq = psm + buf * qk_buf, *dk = dq + TT * Dp;
-    if (vec) {
+    if (vec) {                                     // a warp per token row: no division per copy
       const int per = D >> 2;
-      for (int i = threadIdx.x; i < nt * per; i += PSCAN_THREADS) {
-        const int tt = i / per, p = i % per;
-        cp_async_f4(dq + tt * Dp + 4 * p, qsrc + tt * row + 4 * p);
-        cp_async_f4(dk + tt * Dp + 4 * p, ksrc + tt * row + 4 * p);
-      }
+      for (int tt = threadIdx.x >> 5; tt < nt; tt += PSCAN_THREADS / 32)
+        for (int p = threadIdx.x & 31; p < per; p += 32) {
+          cp_async_f4(dq + tt * Dp + 4 * p, qsrc + tt * row + 4 * p);
+          cp_async_f4(dk + tt * Dp + 4 * p, ksrc + tt * row + 4 * p);
+        }
     } else {
       for (int i = threadIdx.x; i < nt * D; i += PSCAN_THREADS) {
         const int tt = i / D, p = i % D;
@@ -607,9 +608,9 @@ state_scan_prompt_kernel(const PScanArgs a) {
     const float *kp = qp + TT * Dp;
     const float *vp = small + buf * small_buf + col_local;
     const float *gp = small + buf * small_buf + TT * cols, *bp = gp + TT;
-    float *op = a.out + (size_t)(first_row + t0) * out_row + (size_t)h * V + c;
+    float *pp = po + threadIdx.x;
 #pragma unroll 4
-    for (int tt = 0; tt < nt; ++tt, qp += Dp, kp += Dp, vp += cols, op += out_row) {
+    for (int tt = 0; tt < nt; ++tt, qp += Dp, kp += Dp, vp += cols, pp += PSCAN_THREADS) {
       const float v = *vp;
       float o[4] = {0.f, 0.f, 0.f, 0.f};
       if (MODE == 0) {
@@ -653,10 +654,17 @@ state_scan_prompt_kernel(const PScanArgs a) {
           }
         }
       }
-      float osum = (o[0] + o[1]) + (o[2] + o[3]);
+      *pp = (o[0] + o[1]) + (o[2] + o[3]);           // the lanes' shares are added after the tile: nothing waits here
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * cols; i += PSCAN_THREADS) {
+      const int tt = i / cols, cc = i % cols;
+      const float *src = po + tt * PSCAN_THREADS + cc * L;
+      float sum = 0.f;
 #pragma unroll
-      for (int off = L >> 1; off > 0; off >>= 1) osum += __shfl_xor_sync(0xffffffffu, osum, off);
-      if (live && lane_in_col == 0) *op = osum;
+      for (int l = 0; l < L; ++l) sum += src[(l + cc) % L];          // started at another lane per column: no bank conflicts
+      const int col = blockIdx.x * cols + cc;
+      if (col < V) a.out[(size_t)(first_row + t0 + tt) * out_row + (size_t)h * V + col] = sum;
     }
     if (next < n) store_small(nn, buf ^ 1);
   }
@@ -712,7 +720,7 @@ extern "C" int g2b_state_scan_prompt(int mode, int dtype, const void *q, int q_s
   a.Dp = (D + 4 * a.L - 1) / (4 * a.L) * (4 * a.L);
   a.tile = a.Dp <= 128 ? 16 : (a.Dp <= 256 ? 8 : 4);            // q and k of a tile: 16 KB a buffer
   const int cols = PSCAN_THREADS / a.L;
-  const size_t smem = (size_t)(4 * a.tile * a.Dp + 2 * a.tile * (cols + 2)) * sizeof(float);
+  const size_t smem = (size_t)(4 * a.tile * a.Dp + 2 * a.tile * (cols + 2) + a.tile * PSCAN_THREADS) * sizeof(float);
   const dim3 grid((V + cols - 1) / cols, H, n_seqs);
   if (mode == 0) {
     if (dtype == G2B_F32) launch_scan_prompt<float, 0>(a, grid, smem, stream);

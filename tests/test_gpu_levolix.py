@@ -189,7 +189,8 @@ def _attention_part(H, G, D, V, chunk, rot, dtype, width=40, seed=0, zero_q=Fals
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,D,V,chunk,rot", [(4, 2, 16, 24, 16, 8), (3, 1, 64, 64, 128, 64), (2, 2, 24, 8, 24, 24),
-                                               (6, 3, 128, 128, 64, 32)])
+                                               (6, 3, 128, 128, 64, 32), (2, 1, 64, 64, 40, 64), (4, 4, 128, 128, 100, 128),
+                                               (2, 1, 128, 64, 48, 64), (1, 1, 8, 8, 1, 8)])
 def test_chunked_attention_part(H, G, D, V, chunk, rot, dtype):
     """Biases, the norm over the whole projection, interleaved rotation of part of a head, the chunk
     mask, the sink and the gate, over two sequences and every way of cutting them.  Queries are large,
