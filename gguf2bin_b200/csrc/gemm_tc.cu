@@ -229,6 +229,110 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// ---------------------------------------------------------------------------
+// One product per group of rows (a routed feed-forward's experts): rows first .. end of A (and of C)
+// belong to group e and are multiplied by rows e Nw .. (e + 1) Nw of W.  Where the groups lie is a
+// plan in device memory, made by an earlier kernel of the step:
+//   plan[0]            tiles in use;   plan[1 + e] first row of group e;   plan[1 + n_groups] all rows
+//   plan[n_groups + 2 + 3 t ..]  tile t: (group, first row, rows), tiles of `plan rows` rows each
+// The grid has a CTA per plan tile and column tile; a CTA whose plan tile is not the first of a
+// 128-row tile of its group returns at once, the others compute 128 rows from theirs on (rows
+// beyond the group's end are loaded, they are the next group's or zeros, and never stored).
+// ---------------------------------------------------------------------------
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                       void *__restrict__ Cv, const int *__restrict__ plan, int n_groups, int Nw, int K, int ldc,
+                       int *__restrict__ status) {
+  pdl_launch();
+  pdl_wait();                  // the plan is an earlier kernel's output
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int *tl = plan + n_groups + 2 + 3 * tile;
+  const int e = tl[0], m0 = tl[1];
+  const int first = plan[1 + e], end = plan[2 + e];
+  if ((m0 - first) % BM) return;
+  const int m_end = min(m0 + BM, end);
+  const int n0 = blockIdx.x * BN, w0 = e * Nw + n0;
+
+  extern __shared__ unsigned char smem_raw[];
+  using S = Smem<BN, STAGES>;
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::BARRIER_OFFSET);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+  const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
+  const uint32_t acc_bar = smem_addr(bars + 2 * STAGES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                     smem_addr(tmem_slot)), "r"((uint32_t)BN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0 && PRODUCER_RUNS) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !mbar_wait(empty0 + 8 * s, ((kb / STAGES) - 1) & 1)) {
+          atomicExch(status, ST_PRODUCER_TIMEOUT);
+          break;
+        }
+        const uint32_t a_dst = smem_addr(smem + s * S::STAGE_BYTES);
+        mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, kb * BK, m0, full0 + 8 * s);
+        tma_load_2d(a_dst + S::A_BYTES, &map_w, kb * BK, w0, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_n(BN);
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(full0 + 8 * s, (kb / STAGES) & 1)) {
+          atomicExch(status, ST_MMA_TIMEOUT);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t a_addr = smem_addr(smem + s * S::STAGE_BYTES);
+        const uint64_t adesc = desc_k_major(a_addr), bdesc = desc_k_major(a_addr + S::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          umma_bf16(tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);
+      }
+      umma_commit(acc_bar);
+    }
+  } else {
+    if (!mbar_wait(acc_bar, 0)) {
+      if (lane == 0) atomicExch(status, ST_EPILOGUE_TIMEOUT);
+    } else {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      epilogue_tile<BN, EPI>(tmem, reinterpret_cast<float *>(smem) + warp * (32 * 33), Cv, m0, n0, m_end, Nw, ldc, warp, lane);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t)BN));
+  }
+}
+
 // Epilogue of one 128 x BN tile through shared memory and tile stores.  Warp w owns rows
 // 32w .. 32w+31; a thread owns one row.  Per box of 128 bytes per row (64 bfloat16 or 32 float
 // outputs) the thread writes its row into a 32 x 128-byte staging buffer of its warp in the
@@ -1454,6 +1558,49 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
 #undef G2B_SHAPE
 #undef G2B_CASE
   G2B_REFUSE("gemm_tc: no kernel for tile width %d with %d stages and epilogue %d", bn, stages, epi);
+}
+
+template <int BN, int STAGES, int EPI>
+static int launch_grouped(const CUtensorMap &ma, const CUtensorMap &mw, void *C, const int *plan, int n_groups, int Nw,
+                          int K, int ldc, int max_tiles, int *status, cudaStream_t stream) {
+  static G2bPerDevice configured;
+  const int smem = Smem<BN, STAGES>::TOTAL;
+  const int cfg_dev = g2b_current_device();
+  if (cfg_dev < 0 || !configured.value[cfg_dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_grouped_kernel<BN, STAGES, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
+    if (cfg_dev >= 0) configured.value[cfg_dev] = 1;
+  }
+  dim3 grid((Nw + BN - 1) / BN, max_tiles);
+  g2b_launch(gemm_tc_grouped_kernel<BN, STAGES, EPI>, grid, dim3(THREADS), smem, stream, ma, mw, C, plan, n_groups, Nw, K,
+             ldc, status);
+  return g2b_check_launch("gemm_tc (grouped)");
+}
+
+// A [rows, K] (rows sorted by group as the plan says), W [n_groups * Nw, K], C [rows, Nw] float
+// (epi = EPI_STORE_F32) or [rows, Nw / 2] bfloat16 (EPI_SWIGLU_BF16: W's rows alternate eight
+// gates and eight ups).
+extern "C" int g2b_gemm_tc_grouped(const void *A, const void *W, void *C, int rows, int n_groups, int Nw, int K,
+                                   int lda, int ldc, int epi, const int *plan, int max_tiles, int *status,
+                                   cudaStream_t stream) {
+  if (rows <= 0 || Nw <= 0 || n_groups <= 0 || max_tiles <= 0) return 0;
+  if (K <= 0 || K % 8 || lda % 8) G2B_REFUSE("gemm_tc: K=%d and the row stride %d must be multiples of 8", K, lda);
+  if (((uintptr_t)A | (uintptr_t)W) & 15) G2B_REFUSE("gemm_tc: operands must be 16-byte aligned");
+  if (epi == EPI_SWIGLU_BF16 && Nw % 16) G2B_REFUSE("gemm_tc: gated output needs N %% 16 == 0, N=%d", Nw);
+  if (max_tiles > 65535) G2B_REFUSE("gemm_tc: %d row tiles are too many for one launch", max_tiles);
+  if (!status || !plan) G2B_REFUSE("gemm_tc: no status word or no plan");
+  if ((long long)n_groups * Nw > 0x7fffffffLL) G2B_REFUSE("gemm_tc: %d groups of %d rows of W", n_groups, Nw);
+  CUtensorMap ma, mw;
+  int rc = make_map(&ma, A, rows, K, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, n_groups * Nw, K, K, 128);
+  if (rc) return rc;
+  if (epi == EPI_SWIGLU_BF16)
+    return launch_grouped<128, 6, EPI_SWIGLU_BF16>(ma, mw, C, plan, n_groups, Nw, K, ldc, max_tiles, status, stream);
+  if (epi == EPI_STORE_F32)
+    return launch_grouped<128, 6, EPI_STORE_F32>(ma, mw, C, plan, n_groups, Nw, K, ldc, max_tiles, status, stream);
+  G2B_REFUSE("gemm_tc: the grouped kernel stores float or gated bfloat16, not epilogue %d", epi);
 }
 
 #ifdef G2B_GEMM_TIMING

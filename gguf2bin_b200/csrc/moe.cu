@@ -25,6 +25,46 @@ G2B_DEFINE_LAST_ERROR
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 
+// Row of a gate/up matrix [2N, K] that holds gate (s = 0) or up (s = 1) row n: all gates and then all ups
+// (`blocked` = 0), or eight gates and the eight ups of the same outputs in turn (`blocked` = 1, the
+// layout whose neighbours a tensor-core epilogue combines).  Plain matrices pass s = 0, blocked = 0.
+__device__ __forceinline__ size_t gu_row(int s, int n, int N, int blocked) {
+  return blocked ? (size_t)((n >> 3) << 4) + (s << 3) + (n & 7) : (size_t)s * N + n;
+}
+
+// rows gathered side by side, in the plan's order, for the kernels that fetch tiles by address
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const T *__restrict__ A, int a_stride, const int *__restrict__ row_pair, int pairs_per_token,
+                  const int *__restrict__ plan, int n_real, int K, T *__restrict__ out) {
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x;
+  if (r >= plan[1 + n_real]) return;
+  const T *src = A + (size_t)(row_pair[r] / pairs_per_token) * a_stride;
+  T *dst = out + (size_t)r * K;
+  if ((K * sizeof(T)) % 16 == 0 && (a_stride * sizeof(T)) % 16 == 0) {
+    const int n16 = K * (int)sizeof(T) / 16;
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) ((uint4 *)dst)[i] = ((const uint4 *)src)[i];
+  } else {
+    for (int i = threadIdx.x; i < K; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+extern "C" int g2b_moe_gather(const void *A, int dtype, int a_stride, const int *row_pair, int pairs_per_token,
+                              const int *plan, int n_real, int n_rows, int K, void *out, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dtype == G2B_F32)
+    g2b_launch(moe_gather_kernel<float>, dim3(n_rows), dim3(256), 0, stream, (const float *)A, a_stride, row_pair,
+               pairs_per_token, plan, n_real, K, (float *)out);
+  else if (dtype == G2B_BF16)
+    g2b_launch(moe_gather_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, (const bf16 *)A, a_stride, row_pair,
+               pairs_per_token, plan, n_real, K, (bf16 *)out);
+  else
+    G2B_REFUSE("moe_gather: unknown dtype %d", dtype);
+  return g2b_check_launch("moe_gather");
+}
+
 // ---------------------------------------------------------------------------
 // router
 // ---------------------------------------------------------------------------
@@ -163,7 +203,7 @@ template <typename T, bool SWIGLU>
 __global__ void __launch_bounds__(128)
 moe_gemm_kernel(const T *__restrict__ A, int a_stride, const int *__restrict__ row_pair, int pairs_per_token,
                 const T *__restrict__ W, int N, int K, const int *__restrict__ plan, int n_real,
-                void *__restrict__ out, int out_f32) {
+                void *__restrict__ out, int out_f32, int blocked) {
   pdl_launch();
   pdl_wait();
   const int tile = blockIdx.y;
@@ -200,8 +240,8 @@ moe_gemm_kernel(const T *__restrict__ A, int a_stride, const int *__restrict__ r
     for (int i = tid; i < MG_BN * MG_BK; i += 128) {
       const int c = i / MG_BK, kk = i % MG_BK;
       const bool in = n0 + c < N && k0 + kk < K;
-      Bs[0][kk][c] = in ? to_f32(We[(size_t)(n0 + c) * K + k0 + kk]) : 0.f;
-      if (SWIGLU) Bs[1][kk][c] = in ? to_f32(We[((size_t)N + n0 + c) * K + k0 + kk]) : 0.f;
+      Bs[0][kk][c] = in ? to_f32(We[gu_row(0, n0 + c, N, SWIGLU ? blocked : 0) * K + k0 + kk]) : 0.f;
+      if (SWIGLU) Bs[1][kk][c] = in ? to_f32(We[gu_row(1, n0 + c, N, blocked) * K + k0 + kk]) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -248,7 +288,7 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16 *__restrict__ A, int a_stride, const int *__restrict__ row_pair, int pairs_per_token,
                     const bf16 *__restrict__ W, int N, int K, const int *__restrict__ plan, int n_real,
-                    void *__restrict__ out, int out_f32) {
+                    void *__restrict__ out, int out_f32, int blocked) {
   pdl_launch();
   pdl_wait();
   const int tile = blockIdx.y;
@@ -289,7 +329,7 @@ moe_gemm_mma_kernel(const bf16 *__restrict__ A, int a_stride, const int *__restr
     for (int i = tid; i < S * MG_BN * (MT_BK / 8); i += 128) {
       const int s = i / (MG_BN * (MT_BK / 8)), c = (i / (MT_BK / 8)) % MG_BN, p = i % (MT_BK / 8);
       uint4 v = zero;
-      if (n0 + c < N && k0 + p * 8 < K) v = *(const uint4 *)(We + ((size_t)s * N + n0 + c) * K + k0 + p * 8);
+      if (n0 + c < N && k0 + p * 8 < K) v = *(const uint4 *)(We + gu_row(s, n0 + c, N, SWIGLU ? blocked : 0) * K + k0 + p * 8);
       *(uint4 *)&Bs[s][c][p * 8] = v;
     }
     __syncthreads();
@@ -346,7 +386,7 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(256)
 moe_gemm_wide_kernel(const bf16 *__restrict__ A, int a_stride, const int *__restrict__ row_pair, int pairs_per_token,
                      const bf16 *__restrict__ W, int N, int K, const int *__restrict__ plan, int n_real,
-                     void *__restrict__ out, int out_f32) {
+                     void *__restrict__ out, int out_f32, int blocked) {
   pdl_launch();
   pdl_wait();
   constexpr int S = SWIGLU ? 2 : 1;
@@ -397,7 +437,7 @@ moe_gemm_wide_kernel(const bf16 *__restrict__ A, int a_stride, const int *__rest
     for (int i = tid; i < S * MG_BN * (MW_BK / 8); i += 256) {
       const int s = i / (MG_BN * 4), c = (i >> 2) % MG_BN, p = i & 3;
       bf16 *dst = &Bs[st][s][c][p * 8];
-      if (n0 + c < N && k0 + p * 8 < K) cp_async_16(smem_u32(dst), We + ((size_t)s * N + n0 + c) * K + k0 + p * 8);
+      if (n0 + c < N && k0 + p * 8 < K) cp_async_16(smem_u32(dst), We + gu_row(s, n0 + c, N, SWIGLU ? blocked : 0) * K + k0 + p * 8);
       else *(uint4 *)dst = zero;
     }
     cp_async_commit();
@@ -476,7 +516,7 @@ template <typename T, bool SWIGLU>
 __global__ void __launch_bounds__(128)
 moe_gemv_kernel(const T *__restrict__ A, int a_stride, const int *__restrict__ row_pair, int pairs_per_token, int gather,
                 const int *__restrict__ idx, const T *__restrict__ W, int N, int K, const int *__restrict__ plan,
-                int n_real, void *__restrict__ out, int out_f32) {
+                int n_real, void *__restrict__ out, int out_f32, int blocked) {
   pdl_launch();
   pdl_wait();
   const int r = blockIdx.y;
@@ -504,7 +544,7 @@ moe_gemv_kernel(const T *__restrict__ A, int a_stride, const int *__restrict__ r
 #pragma unroll
       for (int j = 0; j < MV_COLS; ++j) {
         const int n = min(n0 + j, N - 1);
-        w[s][j] = *(const uint4 *)(We + ((size_t)s * N + n) * K + (size_t)c * EPL);
+        w[s][j] = *(const uint4 *)(We + gu_row(s, n, N, SWIGLU ? blocked : 0) * K + (size_t)c * EPL);
       }
 #pragma unroll
     for (int s = 0; s < (SWIGLU ? 2 : 1); ++s)
@@ -528,65 +568,65 @@ extern "C" int g2b_moe_tile_rows() { return MG_BM; }
 template <typename T>
 static void launch_gemv(const void *A, int a_stride, const int *row_pair, int pairs_per_token, int gather, const int *idx,
                         const void *W, int N, int K, const int *plan, int n_real, int n_rows, int swiglu, void *out,
-                        int out_f32, cudaStream_t stream) {
+                        int out_f32, int blocked, cudaStream_t stream) {
   const dim3 grid((N + 4 * MV_COLS - 1) / (4 * MV_COLS), n_rows);
   if (swiglu)
     g2b_launch(moe_gemv_kernel<T, true>, grid, dim3(128), 0, stream, (const T *)A, a_stride, row_pair, pairs_per_token,
-               gather, idx, (const T *)W, N, K, plan, n_real, out, out_f32);
+               gather, idx, (const T *)W, N, K, plan, n_real, out, out_f32, blocked);
   else
     g2b_launch(moe_gemv_kernel<T, false>, grid, dim3(128), 0, stream, (const T *)A, a_stride, row_pair, pairs_per_token,
-               gather, idx, (const T *)W, N, K, plan, n_real, out, out_f32);
+               gather, idx, (const T *)W, N, K, plan, n_real, out, out_f32, blocked);
 }
 
 // Few rows: `row_pair` (row -> pair) and `idx` (pair -> expert) are both needed; `gather` says whether
 // row r reads A[pair / pairs_per_token] or A[r].
 extern "C" int g2b_moe_gemv(const void *A, int dtype, int a_stride, const int *row_pair, int pairs_per_token, int gather,
                             const int *idx, const void *W, int N, int K, const int *plan, int n_real, int n_rows,
-                            int swiglu, void *out, int out_f32, cudaStream_t stream) {
+                            int swiglu, void *out, int out_f32, int blocked, cudaStream_t stream) {
   if (n_rows <= 0 || N <= 0) return 0;
   const int epl = dtype == G2B_BF16 ? 8 : 4;
   if (K % epl || a_stride % epl || (((uintptr_t)A | (uintptr_t)W) & 15))
     G2B_REFUSE("moe_gemv: K = %d or the rows' distance %d is no multiple of %d, or a pointer is off 16 bytes", K, a_stride, epl);
-  if (dtype == G2B_F32) launch_gemv<float>(A, a_stride, row_pair, pairs_per_token, gather, idx, W, N, K, plan, n_real, n_rows, swiglu, out, out_f32, stream);
-  else if (dtype == G2B_BF16) launch_gemv<bf16>(A, a_stride, row_pair, pairs_per_token, gather, idx, W, N, K, plan, n_real, n_rows, swiglu, out, out_f32, stream);
+  if (dtype == G2B_F32) launch_gemv<float>(A, a_stride, row_pair, pairs_per_token, gather, idx, W, N, K, plan, n_real, n_rows, swiglu, out, out_f32, blocked, stream);
+  else if (dtype == G2B_BF16) launch_gemv<bf16>(A, a_stride, row_pair, pairs_per_token, gather, idx, W, N, K, plan, n_real, n_rows, swiglu, out, out_f32, blocked, stream);
   else G2B_REFUSE("moe_gemv: unknown dtype %d", dtype);
   return g2b_check_launch("moe_gemv");
 }
 
 extern "C" int g2b_moe_gemm(const void *A, int dtype, int a_stride, const int *row_pair, int pairs_per_token,
                             const void *W, int N, int K, const int *plan, int n_real, int max_tiles, int swiglu,
-                            void *out, int out_f32, cudaStream_t stream) {
+                            void *out, int out_f32, int blocked, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return 0;
   const dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
   if (dtype == G2B_F32) {
     if (swiglu)
       g2b_launch(moe_gemm_kernel<float, true>, grid, dim3(128), 0, stream, (const float *)A, a_stride, row_pair,
-                 pairs_per_token, (const float *)W, N, K, plan, n_real, out, out_f32);
+                 pairs_per_token, (const float *)W, N, K, plan, n_real, out, out_f32, blocked);
     else
       g2b_launch(moe_gemm_kernel<float, false>, grid, dim3(128), 0, stream, (const float *)A, a_stride, row_pair,
-                 pairs_per_token, (const float *)W, N, K, plan, n_real, out, out_f32);
+                 pairs_per_token, (const float *)W, N, K, plan, n_real, out, out_f32, blocked);
   } else if (dtype == G2B_BF16) {
     const bool mma = K % 8 == 0 && a_stride % 8 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0;
     // many rows an expert (a prompt step): the wide tiles
     const bool wide = mma && max_tiles > 3 * n_real + 8;
     if (wide && swiglu)
       g2b_launch(moe_gemm_wide_kernel<true>, grid, dim3(256), 0, stream, (const bf16 *)A, a_stride, row_pair,
-                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32, blocked);
     else if (wide)
       g2b_launch(moe_gemm_wide_kernel<false>, grid, dim3(256), 0, stream, (const bf16 *)A, a_stride, row_pair,
-                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32, blocked);
     else if (mma && swiglu)
       g2b_launch(moe_gemm_mma_kernel<true>, grid, dim3(128), 0, stream, (const bf16 *)A, a_stride, row_pair,
-                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32, blocked);
     else if (mma)
       g2b_launch(moe_gemm_mma_kernel<false>, grid, dim3(128), 0, stream, (const bf16 *)A, a_stride, row_pair,
-                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32, blocked);
     else if (swiglu)
       g2b_launch(moe_gemm_kernel<bf16, true>, grid, dim3(128), 0, stream, (const bf16 *)A, a_stride, row_pair,
-                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32, blocked);
     else
       g2b_launch(moe_gemm_kernel<bf16, false>, grid, dim3(128), 0, stream, (const bf16 *)A, a_stride, row_pair,
-                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32);
+                 pairs_per_token, (const bf16 *)W, N, K, plan, n_real, out, out_f32, blocked);
   } else {
     G2B_REFUSE("moe_gemm: unknown dtype %d", dtype);
   }

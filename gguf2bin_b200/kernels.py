@@ -20,7 +20,7 @@ __all__ = ["KernelError", "KernelBuildError", "embed_rows", "rmsnorm", "qknorm_r
            "attention", "sample_rows", "sample_filtered", "recent_set", "seed_slots", "embed_pair_norm",
            "canon_conv", "norm_canon_single", "latent_keep", "head_product", "head_gate", "gated_add", "xielu",
            "proj_norm_rope_cache", "rotate_heads", "short_conv", "state_scan", "head_norm_gate", "gate_mul",
-           "norm_add", "moe_route", "moe_plan", "moe_gemm", "moe_gemv", "moe_combine", "moe_tile_rows"]
+           "norm_add", "moe_route", "moe_plan", "moe_gemm", "moe_gemv", "moe_gather", "moe_gemm_tc", "moe_combine", "moe_tile_rows"]
 
 F32, BF16 = 0, 1
 EPI_STORE_F32, EPI_STORE_BF16, EPI_ACCUM_F32 = 0, 1, 2
@@ -731,21 +731,22 @@ def moe_plan(idx, n_real: int, max_tiles: int, plan, row_pair, pair_row) -> None
 
 
 def moe_gemm(a, row_pair, pairs_per_token: int, w, n_out: int, plan, n_real: int, max_tiles: int, swiglu: bool,
-             out) -> None:
-    """Per expert e over its rows: out[row] = a[source of row] . w[e]^T; ``w`` [E, n_out (x2: gate rows
-    then up rows, with ``swiglu``), K]; ``row_pair`` None: row r reads a[r]."""
+             out, blocked: bool = False) -> None:
+    """Per expert e over its rows: out[row] = a[source of row] . w[e]^T; ``w`` [E, n_out (x2 with
+    ``swiglu``: gate rows then up rows, or, ``blocked``, eight gates and eight ups in turn), K];
+    ``row_pair`` None: row r reads a[r]."""
     if w.dtype != a.dtype:
         raise KernelError("moe_gemm: activations and expert matrices must have one dtype")
     f = _fn("moe.cu", "g2b_moe_gemm",
             [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
-             c_void_p, c_int, c_void_p])
+             c_void_p, c_int, c_int, c_void_p])
     _call(f, _ptr(a), _code(a.dtype), _dense_rows(a, "a"), _ptr(row_pair), pairs_per_token, _ptr(w), n_out,
           a.shape[1], _ptr(plan), n_real, max_tiles, 1 if swiglu else 0, _ptr(out),
-          1 if out.dtype == torch.float32 else 0, _stream())
+          1 if out.dtype == torch.float32 else 0, 1 if blocked else 0, _stream())
 
 
 def moe_gemv(a, row_pair, pairs_per_token: int, gather: bool, idx, w, n_out: int, plan, n_real: int, n_rows: int,
-             swiglu: bool, out) -> bool:
+             swiglu: bool, out, blocked: bool = False) -> bool:
     """``moe_gemm`` for a step of few rows: a warp per four output columns of one row, the weight rows
     streamed with 16-byte loads.  ``gather``: row r reads a[pair / pairs_per_token], else a[r].  False
     when the sizes do not allow 16-byte loads (the caller then takes ``moe_gemm``)."""
@@ -756,11 +757,30 @@ def moe_gemv(a, row_pair, pairs_per_token: int, gather: bool, idx, w, n_out: int
         return False
     f = _fn("moe.cu", "g2b_moe_gemv",
             [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
-             c_int, c_void_p, c_int, c_void_p])
+             c_int, c_void_p, c_int, c_int, c_void_p])
     _call(f, _ptr(a), _code(a.dtype), _dense_rows(a, "a"), _ptr(row_pair), pairs_per_token, 1 if gather else 0,
           _ptr(idx), _ptr(w), n_out, a.shape[1], _ptr(plan), n_real, n_rows, 1 if swiglu else 0, _ptr(out),
-          1 if out.dtype == torch.float32 else 0, _stream())
+          1 if out.dtype == torch.float32 else 0, 1 if blocked else 0, _stream())
     return True
+
+
+def moe_gather(a, row_pair, pairs_per_token: int, plan, n_real: int, out) -> None:
+    """out[r] = a[row_pair[r] / pairs_per_token] for the rows the plan has in use."""
+    if out.dtype != a.dtype or not out.is_contiguous():
+        raise KernelError("moe_gather: one dtype, a contiguous output")
+    f = _fn("moe.cu", "g2b_moe_gather",
+            [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _call(f, _ptr(a), _code(a.dtype), _dense_rows(a, "a"), _ptr(row_pair), pairs_per_token, _ptr(plan), n_real,
+          out.shape[0], a.shape[1], _ptr(out), _stream())
+
+
+def moe_gemm_tc(a_rows, w, n_out: int, plan, n_real: int, max_tiles: int, swiglu: bool, out) -> bool:
+    """``moe_gemm`` on the tcgen05 kernel: ``a_rows`` [rows, K] bfloat16, gathered in the plan's order;
+    ``w`` [E, n_out (x2, blocked, with ``swiglu``), K]; out float32 [rows, n_out], or bfloat16 with
+    ``swiglu``.  False when the sizes do not fit the kernel."""
+    if a_rows.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    return (_bf16 or _bf16_mod()).gemm_tc_grouped(a_rows, w, n_out, plan, n_real, max_tiles, swiglu, out)
 
 
 def moe_combine(rows32, pair_row, weight, x_self32, top: int, out32) -> None:

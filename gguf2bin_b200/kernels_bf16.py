@@ -126,6 +126,28 @@ def _gemm_tc(a, w, out, epi, bn: int = 0, stages: int = 0, persistent=False, def
           _ptr(_status_word(a.device)), _stream())
 
 
+def gemm_tc_grouped(a_rows, w, n_out: int, plan, n_groups: int, max_tiles: int, swiglu: bool, out) -> bool:
+    """One product per group of rows on the tcgen05 kernel (see ``g2b_gemm_tc_grouped``); False when
+    the sizes or alignments do not fit (the caller has other kernels)."""
+    K = a_rows.shape[1]
+    n_w = (2 if swiglu else 1) * n_out
+    if K % 8 or not a_rows.is_contiguous() or not w.is_contiguous() or a_rows.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    if swiglu and (n_w % 16 or out.dtype != torch.bfloat16 or out.stride(0) % 8 or out.data_ptr() % 16):
+        return False
+    if not swiglu and out.dtype != torch.float32:
+        return False
+    if max_tiles > 65535:
+        return False
+    f = _fn("gemm_tc.cu", "g2b_gemm_tc_grouped",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+             c_void_p, c_void_p])
+    _call(f, _ptr(a_rows), _ptr(w), _ptr(out), a_rows.shape[0], n_groups, n_w, K, a_rows.stride(0), out.stride(0),
+          EPI_SWIGLU_BF16 if swiglu else EPI_STORE_F32, _ptr(plan), max_tiles, _ptr(_status_word(a_rows.device)),
+          _stream())
+    return True
+
+
 _routes: dict = {}        # (sizes, strides, alignment, output) -> (kernel, tile width, stages, persistent)
 
 

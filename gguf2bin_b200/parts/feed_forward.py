@@ -161,6 +161,7 @@ class RoutedExperts:
     comes back to the host, so the step may be replayed from a CUDA graph."""
     graph_safe = True
     FEW_ROWS = 128            # (token, choice) pairs up to which every row streams its expert's matrices by itself
+    MANY_ROWS = 48            # rows an expert on average from which its product runs on the tcgen05 kernel
 
     def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
         self.E, self.I = int(spec["n_experts"]), int(spec.get("n_identity") or 0)
@@ -172,6 +173,7 @@ class RoutedExperts:
             raise ConfigError(f"routed_experts: {self.top} choices among {self.E} + {self.I} experts")
         self.names = dict(spec["names"])
         self.w_router = self.correction = self.w_gate_up = self.w_down = None
+        self.blocked = False
 
     @classmethod
     def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
@@ -194,10 +196,17 @@ class RoutedExperts:
         if self.E:
             mats = [tensors[n[k].format(e)] for e in range(self.E) for k in ("gate", "up", "down")]
             common = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
-            # per expert: gate rows, then up rows
-            self.w_gate_up = torch.stack([torch.cat([tensors[n["gate"].format(e)].to(common),
-                                                     tensors[n["up"].format(e)].to(common)], dim=0)
-                                          for e in range(self.E)]).contiguous()
+            # per expert: eight gate rows and the eight up rows of the same outputs in turn (the layout
+            # whose neighbours the tensor-core epilogue combines); all gates, then all ups, where the
+            # experts' size is no multiple of eight
+            self.blocked = self.inter % 8 == 0
+            b = 8 if self.blocked else self.inter
+
+            def gate_up(e):
+                g, u = tensors[n["gate"].format(e)].to(common), tensors[n["up"].format(e)].to(common)
+                return torch.stack([g.view(self.inter // b, b, self.hidden), u.view(self.inter // b, b, self.hidden)],
+                                   dim=1).reshape(2 * self.inter, self.hidden)
+            self.w_gate_up = torch.stack([gate_up(e) for e in range(self.E)]).contiguous()
             self.w_down = torch.stack([tensors[n["down"].format(e)].to(common) for e in range(self.E)]).contiguous()
 
     def weights(self):
@@ -236,13 +245,29 @@ class RoutedExperts:
             wt = self.w_gate_up.dtype                     # matrices stored in 32-bit keep their products there
             mid = ws.buffer("moe.mid", (n_pairs, self.inter), wt)
             a = h if h.dtype == wt else h.to(wt)
-            # few rows (decoding): every row streams its expert's matrices; else tiles of rows per expert
+            # few rows (decoding): every row streams its expert's matrices.  Many rows an expert (a prompt
+            # step in bfloat16): the rows gathered side by side, then the tcgen05 kernel over each expert's
+            # range.  Else tiles of rows per expert on mma.sync or the CUDA cores.
             few = n_pairs <= self.FEW_ROWS
-            if not (few and kernels.moe_gemv(a, row_pair, top, True, idx, self.w_gate_up, self.inter, plan, E,
-                                             n_pairs, True, mid)):
-                kernels.moe_gemm(a, row_pair, top, self.w_gate_up, self.inter, plan, E, max_tiles, True, mid)
-            if not (few and kernels.moe_gemv(mid, row_pair, top, False, idx, self.w_down, self.hidden, plan, E,
-                                             n_pairs, False, rows32)):
+            many = not few and wt == torch.bfloat16 and self.blocked and n_pairs >= self.MANY_ROWS * max(E, 1)
+            done = False
+            if few:
+                done = kernels.moe_gemv(a, row_pair, top, True, idx, self.w_gate_up, self.inter, plan, E, n_pairs,
+                                        True, mid, self.blocked)
+            elif many and self.hidden % 8 == 0:
+                rows = ws.buffer("moe.gathered", (n_pairs, self.hidden), wt)
+                kernels.moe_gather(a, row_pair, top, plan, E, rows)
+                done = kernels.moe_gemm_tc(rows, self.w_gate_up, self.inter, plan, E, max_tiles, True, mid)
+            if not done:
+                kernels.moe_gemm(a, row_pair, top, self.w_gate_up, self.inter, plan, E, max_tiles, True, mid,
+                                 self.blocked)
+            done = False
+            if few:
+                done = kernels.moe_gemv(mid, row_pair, top, False, idx, self.w_down, self.hidden, plan, E, n_pairs,
+                                        False, rows32)
+            elif many:
+                done = kernels.moe_gemm_tc(mid, self.w_down, self.hidden, plan, E, max_tiles, False, rows32)
+            if not done:
                 kernels.moe_gemm(mid, None, 1, self.w_down, self.hidden, plan, E, max_tiles, False, rows32)
         if x_self32 is None:
             x_self32 = h if h.dtype == torch.float32 else h.float()
