@@ -6,9 +6,14 @@ bandwidth or FLOP/s.
     python -m gguf2bin_b200.kernel_bench decode  [--batch 8] [--ctx 3072] [--only NAME] [--layers 28]
     python -m gguf2bin_b200.kernel_bench prefill [--tokens 2048] [--only NAME] [--layers 4]
     python -m gguf2bin_b200.kernel_bench latent-decode | latent-prefill  [--rank 128] ...
+    python -m gguf2bin_b200.kernel_bench state-decode | state-prefill  [--experts 16] [--top 4] [--chunk 512] ...
 
 The ``latent-*`` modes time the kernels of a gated layer with latent attention (``--heads`` heads of
 ``--head-dim`` key and value numbers, ``--rank`` cached numbers per token) at the same geometry.
+
+The ``state-*`` modes time the kernels of layers that keep a matrix state per head (``--heads`` / 2 heads with
+keys of ``--head-dim`` and values of twice that), of attention in chunks of ``--chunk`` keys with the wide
+prologue, and of a routed feed-forward (``--experts`` experts of ``--inter`` / 4 each, ``--top`` choices).
 
 Sizes default to Qwen3-0.6B (width 1024, 16/8 heads of 128, feed-forward 3072, vocabulary
 151936); --hidden/--inter/--heads/--kv-heads/--vocab change them.  Decode kernels run
@@ -298,9 +303,99 @@ def latent(a, single: bool) -> None:
     kernels_bf16.check_status()
 
 
+def state(a, single: bool) -> None:
+    """The kernels of state mixers, chunked attention and routed experts: ``single``: a decode step of
+    ``--batch`` sequences behind ``--ctx`` tokens; else one prompt of ``--tokens`` tokens."""
+    from .engine.workspace import Workspace as WS
+    from .parts.base import StepContext
+    Lw, W = a.layers, a.hidden
+    H, D, V = max(1, a.heads // 2), a.head_dim, 2 * a.head_dim          # state heads
+    nh, nkv, hd = a.heads, a.kv_heads, a.head_dim                      # attention heads
+    E, top, ff = a.experts, a.top, max(8, a.inter // 4)
+    B = a.batch if single else 1
+    n = 1 if single else a.tokens
+    T, past = B * n, (a.ctx if single else 0)
+    b = Bench(a)
+    ps = 64
+    pages_per = -(-(past + n) // ps)
+    table = torch.arange(B * pages_per, dtype=torch.int32, device=DEV).view(B, pages_per)
+    pos = (torch.arange(n, dtype=torch.int32, device=DEV) + past).repeat(B)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV).repeat_interleave(n)
+    wide = sorted([(s, s * n + r0, min(128, n - r0), past + r0) for s in range(B) for r0 in range(0, n, 128)],
+                  key=lambda t: -(t[3] + t[2]))
+    meta = torch.tensor([[s * n, n, past, s] for s in range(B)], dtype=torch.int32, device=DEV)
+    ctx = StepContext(n_tokens=T, n_seqs=B, tok_ids=pos, tok_pos=pos, tok_seq=seq, page_table=table, page_size=ps,
+                      workspace=WS(DEV), dtype=torch.bfloat16, q_lens=[n] * B, past_lens=[past] * B, slots=list(range(B)),
+                      max_kv_len=pages_per * ps, kv_len_hint=past + n, seq_meta=None if single else meta,
+                      seq_slots=torch.arange(B, dtype=torch.int32, device=DEV),
+                      attn_tiles_wide=torch.tensor(wide, dtype=torch.int32, device=DEV), n_attn_tiles_wide=len(wide))
+    f32 = lambda *shape: torch.randn(*shape, device=DEV)
+    # ---- the scans -------------------------------------------------------------------------------
+    q, k, v = bf(T, H * D) * 50, bf(T, H * D) * 50, bf(T, H * V) * 50
+    states = [torch.zeros(B + 1, H, V, D, device=DEV) for _ in range(Lw)]
+    o32 = torch.empty(T, H * V, device=DEV)
+    decay = torch.full((H,), 0.99, device=DEV)
+    ab, a_log, dtb = f32(T, 2 * H), torch.zeros(H, device=DEV), torch.zeros(H, device=DEV)
+    inv = torch.tensor([1e4 ** (-2.0 * j / D) for j in range(D // 2)], device=DEV)
+    rope = ctx.rope_table(inv)
+    state_bytes = 2 * 4 * B * H * V * D + T * (2 * H * D + H * V) * 2 + T * H * V * 4
+    scan_flops = 6.0 * T * H * D * V
+    b.run("scan_decay", lambda: [kernels.state_scan(q, k, v, st, ctx, o32, H, H, D, V, decay=decay, rope=rope, rotary_dim=D,
+                                                    k_scale=D ** -0.5) for st in states], Lw, nbytes=state_bytes, flops=scan_flops)
+    b.run("scan_delta", lambda: [kernels.state_scan(q, k, v, st, ctx, o32, H, H, D, V, ab=ab, a_log=a_log, dt_bias=dtb,
+                                                    q_scale=D ** -0.5, unit_eps=1e-6) for st in states], Lw,
+          nbytes=state_bytes, flops=scan_flops)
+    gate, og = bf(T, H * V), torch.empty(T, H * V, dtype=torch.bfloat16, device=DEV)
+    b.run("head_norm_gate", lambda: kernels.head_norm_gate(o32, H, V, None, 1e-6, gate, 1.0, og), 1, nbytes=T * H * V * 8)
+    C = 2 * H * D + H * V
+    x, y = bf(T, C), torch.empty(T, C, dtype=torch.bfloat16, device=DEV)
+    ring, wc = torch.zeros(B + 1, 4, C, dtype=torch.bfloat16, device=DEV), f32(4, C)
+    b.run("short_conv", lambda: kernels.short_conv(x, wc, ring, ctx, y), 1, nbytes=T * C * 4)
+    x32, y32, nw = f32(T, W), f32(T, W), torch.ones(W, device=DEV)
+    hcast = torch.empty(T, W, dtype=torch.bfloat16, device=DEV)
+    b.run("norm_add", lambda: kernels.norm_add(x32, y32, nw, 1e-6, hcast), 1, nbytes=T * W * 14)
+    # ---- chunked attention with the wide prologue ----------------------------------------------------
+    nq, nk = nh * hd, nkv * hd
+    qkv, bias = bf(T, nq + 2 * nk + nq), f32(nq + 2 * nk)
+    qw, kw = torch.ones(nq, device=DEV), torch.ones(nk, device=DEV)
+    pages = torch.zeros(B * pages_per + 1, 2, nkv, ps, hd, dtype=torch.bfloat16, device=DEV)
+    qo, ao = torch.empty(T, nq, dtype=torch.bfloat16, device=DEV), torch.empty(T, nq, dtype=torch.bfloat16, device=DEV)
+    sink = torch.zeros(nh, device=DEV)
+    b.run("proj_norm_rope_cache", lambda: kernels.proj_norm_rope_cache(qkv, bias, nh, nkv, hd, hd, qw, kw, 1e-6, rope, hd,
+                                                                       True, ctx, pages, ps, qo), 1,
+          nbytes=T * (nq + 2 * nk) * 4)
+    seen = min(a.chunk, past + n)
+    b.run("attention_chunked", lambda: kernels.attention(qo, ao, pages, ctx, nh, nkv, hd, ps, 0, hd ** -0.5, sink=sink,
+                                                         chunk=a.chunk), 1,
+          nbytes=B * 2 * nk * 2 * ((past + n - 1) % a.chunk + 1) if single else None,
+          flops=None if single else 4.0 * nq * sum(min(t % a.chunk, t) + 1 for t in range(n)))
+    # ---- routed experts -------------------------------------------------------------------------------
+    from .config.specs import PartSpec
+    from .parts.feed_forward import RoutedExperts
+    spec = PartSpec.make("routed_experts", n_experts=E, n_identity=0, top=top, intermediate_size=ff, correction=False,
+                         names=(("router", "r"), ("gate", "e{}.g"), ("up", "e{}.u"), ("down", "e{}.d")))
+    parts = []
+    for _ in range(min(Lw, 4)):
+        part = RoutedExperts(spec, W, torch.bfloat16, DEV)
+        t = {"r": bf(E, W)}
+        for e in range(E):
+            t[f"e{e}.g"], t[f"e{e}.u"], t[f"e{e}.d"] = bf(ff, W), bf(ff, W), bf(W, ff)
+        part.bind(t)
+        parts.append(part)
+    h = bf(T, W) * 50
+    out32 = torch.empty(T, W, device=DEV)
+    touched = min(E, T * top)
+    b.run("routed_experts (route, plan, products, sum)", lambda: [p.forward_into(h, ctx, out32, x32) for p in parts], len(parts),
+          nbytes=3 * touched * ff * W * 2 if single else None, flops=None if single else 6.0 * T * top * ff * W)
+    kernels_bf16.check_status()
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("mode", choices=["decode", "prefill", "latent-decode", "latent-prefill"])
+    ap.add_argument("mode", choices=["decode", "prefill", "latent-decode", "latent-prefill", "state-decode", "state-prefill"])
+    ap.add_argument("--experts", type=int, default=16, help="state modes: experts of the routed feed-forward")
+    ap.add_argument("--top", type=int, default=4, help="state modes: experts a token uses")
+    ap.add_argument("--chunk", type=int, default=512, help="state modes: keys a chunk of the attention holds")
     ap.add_argument("--rank", type=int, default=128, help="latent modes: cached numbers per token")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=3072)
@@ -317,7 +412,9 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     if a.layers is None:
         a.layers = 28 if a.mode.endswith("decode") else 4
-    if a.mode.startswith("latent"):
+    if a.mode.startswith("state"):
+        state(a, a.mode == "state-decode")
+    elif a.mode.startswith("latent"):
         latent(a, a.mode == "latent-decode")
     else:
         (decode if a.mode == "decode" else prefill)(a)
