@@ -653,6 +653,66 @@ moe_combine_kernel(const float *__restrict__ rows, const int *__restrict__ pair_
   }
 }
 
+// The combination, then the sum's RMS norm (times a weight) added to the stream, and the new stream
+// once more in the compute type: what a layer whose sublayer outputs are normed does behind its routed
+// feed-forward, in one pass.  A thread keeps its share of the row (rows of up to 4,096 entries).
+#define MCN_PER 16
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_norm_add_kernel(const float *__restrict__ rows, const int *__restrict__ pair_row,
+                            const float *__restrict__ weight, float *__restrict__ x, const float *__restrict__ norm_w,
+                            float eps, int top, int Hw, T *__restrict__ cast_out) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  float *xr = x + (size_t)t * Hw;
+  float keep[MCN_PER], own[MCN_PER];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MCN_PER; ++i) {
+    const int j = threadIdx.x + 256 * i;
+    float acc = 0.f;
+    own[i] = 0.f;
+    if (j < Hw) {
+      own[i] = xr[j];
+      for (int r = 0; r < top; ++r) {
+        const int row = pair_row[(size_t)t * top + r];
+        acc = fmaf(weight[(size_t)t * top + r], row >= 0 ? rows[(size_t)row * Hw + j] : own[i], acc);
+      }
+    }
+    keep[i] = acc;
+    ss = fmaf(acc, acc, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)Hw + eps);
+#pragma unroll
+  for (int i = 0; i < MCN_PER; ++i) {
+    const int j = threadIdx.x + 256 * i;
+    if (j < Hw) {
+      const float v = own[i] + (keep[i] * inv) * (norm_w ? norm_w[j] : 1.f);
+      xr[j] = v;
+      if (cast_out) cast_out[(size_t)t * Hw + j] = from_f32<T>(v);
+    }
+  }
+}
+
+extern "C" int g2b_moe_combine_norm_add(const float *rows, const int *pair_row, const float *weight, float *x,
+                                        const float *norm_w, float eps, int T_tokens, int top, int Hw, void *cast_out,
+                                        int dtype, cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (Hw > 256 * MCN_PER) G2B_REFUSE("moe_combine_norm_add: rows of %d entries (at most %d)", Hw, 256 * MCN_PER);
+  if (dtype == G2B_F32)
+    g2b_launch(moe_combine_norm_add_kernel<float>, dim3(T_tokens), dim3(256), 0, stream, rows, pair_row, weight, x, norm_w,
+               eps, top, Hw, (float *)cast_out);
+  else if (dtype == G2B_BF16)
+    g2b_launch(moe_combine_norm_add_kernel<bf16>, dim3(T_tokens), dim3(256), 0, stream, rows, pair_row, weight, x, norm_w,
+               eps, top, Hw, (bf16 *)cast_out);
+  else
+    G2B_REFUSE("moe_combine_norm_add: unknown dtype %d", dtype);
+  return g2b_check_launch("moe_combine_norm_add");
+}
+
 extern "C" int g2b_moe_combine(const float *rows, const int *pair_row, const float *weight, const float *x_self, int T,
                                int top, int Hw, float *out, cudaStream_t stream) {
   if (T <= 0) return 0;

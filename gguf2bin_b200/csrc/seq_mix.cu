@@ -811,6 +811,7 @@ extern "C" int g2b_gate_mul(const void *o, int hd, const void *gate, int gate_st
 // ---------------------------------------------------------------------------
 // x += norm(y) * w; the new x once more in the compute type
 // ---------------------------------------------------------------------------
+#define NORM_ADD_PER 16       // elements a thread keeps of a row of up to 4,096
 template <typename T>
 __global__ void __launch_bounds__(256)
 norm_add_kernel(float *__restrict__ x, const float *__restrict__ y, const float *__restrict__ w, float eps, int Hw,
@@ -820,13 +821,39 @@ norm_add_kernel(float *__restrict__ x, const float *__restrict__ y, const float 
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   float *xr = x + (size_t)t * Hw;
+  const bool held = Hw <= 256 * NORM_ADD_PER;          // the row of y stays in registers: one pass over it
+  float keep[NORM_ADD_PER];
   float inv = 0.f;
   if (y) {
     const float *yr = y + (size_t)t * Hw;
     float ss = 0.f;
-    for (int j = threadIdx.x; j < Hw; j += blockDim.x) ss = fmaf(yr[j], yr[j], ss);
+    if (held) {
+#pragma unroll
+      for (int i = 0; i < NORM_ADD_PER; ++i) {
+        const int j = threadIdx.x + 256 * i;
+        keep[i] = j < Hw ? yr[j] : 0.f;
+        ss = fmaf(keep[i], keep[i], ss);
+      }
+    } else {
+      for (int j = threadIdx.x; j < Hw; j += blockDim.x) ss = fmaf(yr[j], yr[j], ss);
+    }
     ss = block_sum(ss, scratch);
     inv = 1.f / sqrtf(ss / (float)Hw + eps);
+  }
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < NORM_ADD_PER; ++i) {
+      const int j = threadIdx.x + 256 * i;
+      if (j < Hw) {
+        float v = xr[j];
+        if (y) {
+          v += (keep[i] * inv) * (w ? w[j] : 1.f);
+          xr[j] = v;
+        }
+        if (cast_out) cast_out[(size_t)t * Hw + j] = from_f32<T>(v);
+      }
+    }
+    return;
   }
   for (int j = threadIdx.x; j < Hw; j += blockDim.x) {
     float v = xr[j];

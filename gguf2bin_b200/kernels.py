@@ -20,7 +20,7 @@ __all__ = ["KernelError", "KernelBuildError", "embed_rows", "rmsnorm", "qknorm_r
            "attention", "sample_rows", "sample_filtered", "recent_set", "seed_slots", "embed_pair_norm",
            "canon_conv", "norm_canon_single", "latent_keep", "head_product", "head_gate", "gated_add", "xielu",
            "proj_norm_rope_cache", "rotate_heads", "short_conv", "state_scan", "head_norm_gate", "gate_mul",
-           "norm_add", "moe_route", "moe_plan", "moe_gemm", "moe_gemv", "moe_gather", "moe_gemm_tc", "moe_combine", "moe_tile_rows"]
+           "norm_add", "moe_route", "moe_plan", "moe_gemm", "moe_gemv", "moe_gather", "moe_gemm_tc", "moe_combine", "moe_combine_norm_add", "moe_tile_rows"]
 
 F32, BF16 = 0, 1
 EPI_STORE_F32, EPI_STORE_BF16, EPI_ACCUM_F32 = 0, 1, 2
@@ -788,3 +788,19 @@ def moe_combine(rows32, pair_row, weight, x_self32, top: int, out32) -> None:
     f = _fn("moe.cu", "g2b_moe_combine", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
     _call(f, _ptr(rows32), _ptr(pair_row), _ptr(weight), _ptr(x_self32), out32.shape[0], top, out32.shape[1],
           _ptr(out32), _stream())
+
+
+def moe_combine_norm_add(rows32, pair_row, weight, x32, norm_w, eps: float, top: int, cast_out=None) -> bool:
+    """``moe_combine`` whose sum is not stored: x += sum / sqrt(mean(sum^2) + eps) * norm_w, the experts
+    without matrices reading x as it was, and the new x once more, rounded, into ``cast_out``.  False
+    for rows of more than 4,096 entries (the caller then runs the two kernels one after the other)."""
+    if x32.shape[1] > 4096:
+        return False
+    _need(x32, torch.float32, "stream")
+    if norm_w is not None:
+        _need(norm_w, torch.float32, "norm weight")
+    f = _fn("moe.cu", "g2b_moe_combine_norm_add",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p, c_int, c_void_p])
+    _call(f, _ptr(rows32), _ptr(pair_row), _ptr(weight), _ptr(x32), _ptr(norm_w), eps, x32.shape[0], top,
+          x32.shape[1], _ptr(cast_out), _code(cast_out.dtype) if cast_out is not None else F32, _stream())
+    return True

@@ -95,7 +95,8 @@ class BranchNormBlock:
     sublayers read the stream as it is (rounded to the compute type for their products); each
     sublayer's whole output is normed, in 32-bit, before it joins the stream.  A layer may have no
     feed-forward.  Any mixer or feed-forward of the library fits: a part adds into a cleared
-    32-bit buffer, or stores there when it offers ``forward_into``."""
+    32-bit buffer, or stores there when it offers ``forward_store`` (mixers) or ``forward_into``
+    (feed-forwards); routed experts sum, norm and join the stream in one pass (``forward_join``)."""
 
     def __init__(self, layer: LayerSpec, hidden_size: int, dtype: torch.dtype, device):
         self.names = dict(layer.block["names"])
@@ -167,22 +168,30 @@ class BranchNormBlock:
             h = ws.buffer("branch.input", (T, H), self.dtype)
             kernels.norm_add(x32, None, None, 0.0, h)
         y = ws.buffer("branch.result", (T, H), torch.float32)
-        y.zero_()
-        self.mixer.forward(h, ctx, cache_view, y)
+        if hasattr(self.mixer, "forward_store"):       # the mixer's last product stores: no cleared buffer
+            self.mixer.forward_store(h, ctx, cache_view, y)
+        else:
+            y.zero_()
+            self.mixer.forward(h, ctx, cache_view, y)
         last = self.feed_forward is None
         follows = isinstance(getattr(ctx, "next_block", None), BranchNormBlock)
         self._join(x32, y, self.mixer_norm, h if (not last or follows) else None)
         if not last:
             ff = self.feed_forward
-            if hasattr(ff, "forward_into"):
-                if isinstance(ff, RoutedExperts):
+            h_next = h if follows else None
+            joined = False
+            if isinstance(ff, RoutedExperts):
+                if isinstance(self.ffn_norm, RMSNorm):       # the experts' sum, its norm and the addition in one pass
+                    joined = ff.forward_join(h, ctx, x32, self.ffn_norm.weight, self.ffn_norm.eps, h_next)
+                if not joined:
                     ff.forward_into(h, ctx, y, x32)
-                else:
-                    ff.forward_into(h, ctx, y)
+            elif hasattr(ff, "forward_into"):
+                ff.forward_into(h, ctx, y)
             else:
                 y.zero_()
                 ff.forward(h, ctx, y)
-            self._join(x32, y, self.ffn_norm, h if follows else None)
+            if not joined:
+                self._join(x32, y, self.ffn_norm, h_next)
         if follows:
             ctx.step_cache[("branch_norm.rounded", x32.data_ptr())] = h
 

@@ -227,6 +227,22 @@ class RoutedExperts:
     def forward_into(self, h: torch.Tensor, ctx, out32: torch.Tensor, x_self32: torch.Tensor = None) -> None:
         """Stores the result.  ``x_self32``: the input in 32-bit, for the experts whose output is their
         input (default: ``h`` widened)."""
+        rows32, pair_row, weight = self._experts(h, ctx)
+        if x_self32 is None:
+            x_self32 = h if h.dtype == torch.float32 else h.float()
+        kernels.moe_combine(rows32, pair_row, weight, x_self32, self.top, out32)
+
+    def forward_join(self, h: torch.Tensor, ctx, x32: torch.Tensor, norm_w, eps: float, cast_out) -> bool:
+        """For a block that norms the feed-forward's output before it joins the stream ``x32`` (which is
+        also the feed-forward's input in 32-bit): x += sum / sqrt(mean(sum^2) + eps) * norm_w in the
+        pass that sums the experts.  False (nothing done) when the width is beyond that kernel."""
+        if x32.shape[1] > 4096:
+            return False
+        rows32, pair_row, weight = self._experts(h, ctx)
+        return kernels.moe_combine_norm_add(rows32, pair_row, weight, x32, norm_w, eps, self.top, cast_out)
+
+    def _experts(self, h: torch.Tensor, ctx):
+        """Routing, plan and the experts' products: (rows, pair -> row, weights)."""
         T, ws, top, E = h.shape[0], ctx.workspace, self.top, self.E
         z = ws.buffer("moe.logits", (T, E + self.I), torch.float32)
         kernels.linear(h, self.w_router, z)
@@ -269,9 +285,7 @@ class RoutedExperts:
                 done = kernels.moe_gemm_tc(mid, self.w_down, self.hidden, plan, E, max_tiles, False, rows32)
             if not done:
                 kernels.moe_gemm(mid, None, 1, self.w_down, self.hidden, plan, E, max_tiles, False, rows32)
-        if x_self32 is None:
-            x_self32 = h if h.dtype == torch.float32 else h.float()
-        kernels.moe_combine(rows32, pair_row, weight, x_self32, top, out32)
+        return rows32, pair_row, weight
 
 
 register_feed_forward("routed_experts", RoutedExperts)

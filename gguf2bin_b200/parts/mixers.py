@@ -169,6 +169,12 @@ class GQAAttention:
         kernels.linear(h, self.w_qkv, qkv)
         self._attend(qkv, ctx, view, residual32)
 
+    def forward_store(self, h: torch.Tensor, ctx, view: KVView, out32: torch.Tensor) -> None:
+        """Stores the result instead of adding it."""
+        qkv = ctx.workspace.buffer("attn.qkv", (h.shape[0], self.w_qkv.shape[0]), self.dtype)
+        kernels.linear(h, self.w_qkv, qkv)
+        self._attend(qkv, ctx, view, out32, accumulate=False)
+
     def forward_from_stream(self, x32: torch.Tensor, norm, ctx, view: KVView,
                             residual32: torch.Tensor) -> None:
         """The same with the block's norm folded into the q/k/v product."""
@@ -176,7 +182,7 @@ class GQAAttention:
         normed_linear(x32, norm, self.w_qkv, qkv, ctx)
         self._attend(qkv, ctx, view, residual32)
 
-    def _attend_wide(self, qkv: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor) -> None:
+    def _attend_wide(self, qkv: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor, accumulate: bool = True) -> None:
         """q, k, v (and the gate's columns) of one product; the prologue adds the biases, norms all
         of q and all of k, rotates and writes the pages; attention; gate; output product."""
         T, ws = qkv.shape[0], ctx.workspace
@@ -195,11 +201,11 @@ class GQAAttention:
             og = ws.buffer("attn.gated", (T, no), self.dtype)
             kernels.gate_mul(o, hd, gate, self.nh, self.vd, self.out_scale, og)
             o = og
-        kernels.linear(o, self.w_o, residual32, accumulate=True)
+        kernels.linear(o, self.w_o, residual32, accumulate=accumulate)
 
-    def _attend(self, qkv: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor) -> None:
+    def _attend(self, qkv: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor, accumulate: bool = True) -> None:
         if self.wide:
-            return self._attend_wide(qkv, ctx, view, residual32)
+            return self._attend_wide(qkv, ctx, view, residual32, accumulate)
         T = qkv.shape[0]
         nq = self.nh * self.hd
         nkv_own = 0 if self.shared_kv else self.nkv        # kv heads this layer projects
@@ -230,7 +236,7 @@ class GQAAttention:
             og = ws.buffer("attn.gated", (T, nq), self.dtype)
             kernels.gate_mul(o, self.hd, None, self.nh, self.hd, self.out_scale, og)
             o = og
-        kernels.linear(o, self.w_o, residual32, accumulate=True)
+        kernels.linear(o, self.w_o, residual32, accumulate=accumulate)
 
 
 register_mixer("gqa_attention", GQAAttention)

@@ -86,6 +86,13 @@ class RetentionMixer:
         return StateNeed((self.H, self.V, self.D), torch.float32)
 
     def forward(self, h: torch.Tensor, ctx, view, residual32: torch.Tensor) -> None:
+        self._run(h, ctx, view, residual32, True)
+
+    def forward_store(self, h: torch.Tensor, ctx, view, out32: torch.Tensor) -> None:
+        """Stores the result instead of adding it."""
+        self._run(h, ctx, view, out32, False)
+
+    def _run(self, h, ctx, view, residual32, accumulate: bool) -> None:
         T, ws = h.shape[0], ctx.workspace
         nq, nv = self.H * self.D, self.H * self.V
         proj = ws.buffer("retention.in", (T, 2 * nq + 2 * nv), self.dtype)
@@ -98,7 +105,7 @@ class RetentionMixer:
                            interleaved=interleaved, k_scale=self.k_scale)
         og = ws.buffer("retention.gated", (T, nv), self.dtype)
         kernels.head_norm_gate(o32, self.H, self.V, None, self.eps, proj[:, 2 * nq + nv:], self.out_scale, og)
-        kernels.linear(og, self.w_o, residual32, accumulate=True)
+        kernels.linear(og, self.w_o, residual32, accumulate=accumulate)
 
 
 class GatedDeltaMixer:
@@ -162,6 +169,13 @@ class GatedDeltaMixer:
         return need
 
     def forward(self, h: torch.Tensor, ctx, view, residual32: torch.Tensor) -> None:
+        self._run(h, ctx, view, residual32, True)
+
+    def forward_store(self, h: torch.Tensor, ctx, view, out32: torch.Tensor) -> None:
+        """Stores the result instead of adding it."""
+        self._run(h, ctx, view, out32, False)
+
+    def _run(self, h, ctx, view, residual32, accumulate: bool) -> None:
         T, ws = h.shape[0], ctx.workspace
         C, nq, nv = self.channels, self.G * self.D, self.H * self.V
         proj = ws.buffer("delta.in", (T, C + nv), self.dtype)
@@ -177,7 +191,7 @@ class GatedDeltaMixer:
                            q_scale=self.D ** -0.5, unit_eps=self.unit_eps)
         og = ws.buffer("delta.gated", (T, nv), self.dtype)
         kernels.head_norm_gate(o32, self.H, self.V, self.norm_w, self.eps, proj[:, C:], self.out_scale, og)
-        kernels.linear(og, self.w_o, residual32, accumulate=True)
+        kernels.linear(og, self.w_o, residual32, accumulate=accumulate)
 
 
 class ParallelMixer:
@@ -222,11 +236,23 @@ class ParallelMixer:
         return need or None
 
     def forward(self, h: torch.Tensor, ctx, view, residual32: torch.Tensor) -> None:
+        self._run(h, ctx, view, residual32, True)
+
+    def forward_store(self, h: torch.Tensor, ctx, view, out32: torch.Tensor) -> None:
+        """Stores the result: the first branch stores (or adds into the cleared buffer), the others add."""
+        self._run(h, ctx, view, out32, False)
+
+    def _run(self, h, ctx, view, residual32, accumulate: bool) -> None:
         view = view or {}
-        for name, m in self.branches:
+        for i, (name, m) in enumerate(self.branches):
             own = view.get(name)
             if own is None:
                 own = {k[len(name) + 1:]: v for k, v in view.items() if k.startswith(name + ".")} or None
+            if i == 0 and not accumulate:
+                if hasattr(m, "forward_store"):
+                    m.forward_store(h, ctx, own, residual32)
+                    continue
+                residual32.zero_()
             m.forward(h, ctx, own, residual32)
 
 
