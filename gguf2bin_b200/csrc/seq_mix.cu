@@ -187,8 +187,8 @@ short_conv_kernel(const T *__restrict__ x, int x_stride, const float *__restrict
                   T *__restrict__ out, int out_stride) {
   pdl_launch();
   pdl_wait();
-  const int t = blockIdx.y;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int t = blockIdx.x;                        // tokens along x: a step may bring more than 65,535
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const int b = tok_seq[t], pos = tok_pos[t];
   const int first_row = seq_meta ? seq_meta[4 * b + 0] : t;
@@ -228,7 +228,8 @@ extern "C" int g2b_short_conv(const void *x, int dtype, int x_stride, const floa
   if (T_tokens <= 0 || C <= 0) return 0;
   if (taps < 1 || taps > CONV_MAX_TAPS) G2B_REFUSE("short_conv: %d taps outside 1..%d", taps, CONV_MAX_TAPS);
   if (taps > 1 && !ring) G2B_REFUSE("short_conv: no ring for the rows before the step");
-  const dim3 grid((C + 255) / 256, T_tokens), keep_grid((C + 255) / 256, n_seqs);
+  const dim3 grid(T_tokens, (C + 255) / 256), keep_grid((C + 255) / 256, n_seqs);
+  if (grid.y > 65535 || n_seqs > 65535) G2B_REFUSE("short_conv: %d channels or %d sequences are too many for one launch", C, n_seqs);
   if (dtype == G2B_F32) {
     g2b_launch(short_conv_kernel<float>, grid, dim3(256), 0, stream, (const float *)x, x_stride, w, (float *)ring, taps, C,
                T_tokens, tok_pos, tok_seq, seq_slots, seq_meta, act, (float *)out, out_stride);
