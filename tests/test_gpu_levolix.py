@@ -163,6 +163,57 @@ def test_gated_delta_part(H, G, D, V, taps, dtype):
             close(got[b], ref[b], dtype, f"gated delta {cuts[0][:3]} sequence {b}")
 
 
+@pytest.mark.parametrize("kind", ["retention", "gated_delta"])
+def test_a_token_far_back_still_counts(kind):
+    """520 tokens, the first one huge, a head that forgets slowly: 500 in one prompt step (tiles of the
+    prompt scan, the state handed on between them), then 20 one by one.  The plain recurrence says
+    how much of the end's output is the first token's doing; a state lost, cleared or decayed wrongly on
+    the way would miss it by that much."""
+    from gguf2bin_b200.config.specs import PartSpec
+    from gguf2bin_b200.parts.recurrent import GatedDeltaMixer, RetentionMixer
+    rng = np.random.default_rng(11)
+    width, H, D, V = 32, 2, 16, 24
+    h = bf(rng.standard_normal((520, width)))
+    h[0] *= 40.0
+    if kind == "retention":
+        decay = [0.9995, 0.5]
+        m = dict(heads=H, dim=D, vdim=V, decay=decay, rot=dict(dims=D, base=1e4))
+        W = {"q": rng.standard_normal((H * D, width)) / 5, "k": rng.standard_normal((H * D, width)) / 5,
+             "v": rng.standard_normal((H * V, width)) / 5, "g": rng.standard_normal((H * V, width)) / 4,
+             "o": rng.standard_normal((width, H * V)) / np.sqrt(H * V)}
+        W = {k: bf(v) for k, v in W.items()}
+        spec = PartSpec.make("retention", n_heads=H, qk_dim=D, v_dim=V, decay=tuple(decay), eps=EPS,
+                             position=PartSpec.make("rope_neox", theta=1e4, rotary_dim=D),
+                             names=names_of("", (("q", "q"), ("k", "k"), ("v", "v"), ("gate", "g"), ("o", "o"))))
+        part = RetentionMixer(spec, width, torch.float32, DEV)
+        plain = lambda x: LP.retention(x, W, "", m, EPS, np.arange(len(x)))[0]
+    else:
+        m = dict(heads=H, kv_heads=1, dim=D, vdim=V, conv=2)
+        W = {"q": rng.standard_normal((D, width)) / 4, "k": rng.standard_normal((D, width)) / 4,
+             "v": rng.standard_normal((H * V, width)) / 4, "g": rng.standard_normal((H * V, width)) / 4,
+             "q.conv": rng.standard_normal((D, 2)) * 0.7, "k.conv": rng.standard_normal((D, 2)) * 0.7,
+             "v.conv": rng.standard_normal((H * V, 2)) * 0.7, "b": rng.standard_normal((H, width)) / 8 - 0.0,
+             "a": rng.standard_normal((H, width)) / 8, "A_log": np.array([-7.0, 0.0]), "dt_bias": np.zeros(H),
+             "norm": np.ones(V), "o": rng.standard_normal((width, H * V)) / np.sqrt(H * V)}
+        W["b"] = W["b"] * 0 + 0.0                      # write strength one half: later tokens wear the first one down slowly
+        W = {k: bf(v) for k, v in W.items()}
+        keys = (("q", "q"), ("k", "k"), ("v", "v"), ("gate", "g"), ("o", "o"), ("q_conv", "q.conv"), ("k_conv", "k.conv"),
+                ("v_conv", "v.conv"), ("beta", "b"), ("a", "a"), ("a_log", "A_log"), ("dt_bias", "dt_bias"), ("norm", "norm"))
+        spec = PartSpec.make("gated_delta", n_heads=H, n_qk_heads=1, qk_dim=D, v_dim=V, conv_taps=2, eps=EPS,
+                             names=names_of("", keys))
+        part = GatedDeltaMixer(spec, width, torch.float32, DEV)
+        plain = lambda x: LP.delta_rule(x, W, "", m, EPS)[0]
+    part.bind({k: dev(v) for k, v in W.items()})
+    ref = plain(h)
+    without = h.copy()
+    without[0] = 0.0
+    share = np.abs(ref[-20:] - plain(without)[-20:]).max()
+    assert share > 1e-2 * np.abs(ref[-20:]).max()          # the first token is still there at the end
+    got = run_part(part, part.cache_need(), [h], ([500] + [1] * 20,), "float32", slots=(1,), pages_per_seq=10)[0]
+    assert np.abs(got - ref).max() < 1e-3 * share
+    close(got, ref, "float32", f"{kind} over 520 tokens")
+
+
 def _attention_part(H, G, D, V, chunk, rot, dtype, width=40, seed=0, zero_q=False):
     from gguf2bin_b200.config.specs import PartSpec
     from gguf2bin_b200.parts.mixers import GQAAttention
